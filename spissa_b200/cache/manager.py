@@ -32,9 +32,9 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..parts.base import KVCacheRequest, StateRequest
+from ..parts.base import CacheBundle, KVCacheRequest, StateRequest
 from .slots import CacheFull, CacheMisuse, IndexPool
-from .views import KVLayerView, StateLayerView
+from .views import BundleView, KVLayerView, StateLayerView
 
 
 @dataclass
@@ -78,16 +78,17 @@ class KVGroup:
         self.page_size, self.n_pages = page_size, n_pages
         self.pages = IndexPool(n_pages, f"page of cache group {name}")
         shape = (len(self.cache_ids), n_pages, request.num_kv_heads, page_size, request.head_dim)
+        v_shape = shape[:-1] + (request.v_head_dim or request.head_dim,)
         # zeros: a masked key's weight of zero must never meet a NaN left in fresh memory
         self.k = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
+        self.v = torch.zeros(v_shape, dtype=dtype, device=device) if allocate else None
         self.index = {c: i for i, c in enumerate(self.cache_ids)}
 
     def pages_for(self, length: int) -> int:
         return (length + self.page_size - 1) // self.page_size
 
     def bytes(self) -> int:
-        return 0 if self.k is None else 2 * self.k.numel() * self.k.element_size()
+        return 0 if self.k is None else (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class StateGroup:
@@ -121,13 +122,21 @@ class CacheManager:
         self.state_groups: dict = {}
         self.cache_group: dict = {}
         by_need: dict = {}
+        self.bundles: dict = {}                          # cache id -> names of the caches a run asked for together
         for cid, req in requests.items():
             if req is None:
+                continue
+            if isinstance(req, CacheBundle):
+                # each named request becomes a cache of its own under the id (cid, name)
+                self.bundles[cid] = [name for name, _ in req.parts]
+                for name, r in req.parts:
+                    by_need.setdefault(r, []).append((cid, name))
                 continue
             by_need.setdefault(req, []).append(cid)
         for req, cids in by_need.items():
             if isinstance(req, KVCacheRequest):
-                name = f"kv{len(self.kv_groups)}" + (f"_w{req.window}" if req.window else "")
+                name = f"kv{len(self.kv_groups)}" + (f"_w{req.window}" if req.window else "") + \
+                    (f"_f{req.keep_first}" if req.window and req.keep_first else "")
                 self.kv_groups[name] = KVGroup(name, req, cids, self.n_pages, page_size, dtype, device, allocate)
             elif isinstance(req, StateRequest):
                 name = f"state{len(self.state_groups)}"
@@ -247,7 +256,8 @@ class CacheManager:
                 # the next query stands at ``after`` and sees keys >= after - w + 1
                 first_needed = max(0, after - w + 1) // self.page_size
                 pages = seq.pages[g.name]
-                for i in range(min(first_needed, len(pages))):
+                kept = g.pages_for(g.request.keep_first)      # pages of the first positions that stay visible
+                for i in range(min(kept, first_needed), min(first_needed, len(pages))):
                     if pages[i] is not None:
                         g.pages.release(pages[i])
                         pages[i] = None
@@ -316,7 +326,9 @@ class CacheManager:
                 seq.draws += 1
 
     # ------------------------------------------------------------------ views
-    def view(self, cache_id: int, step, writes: bool):
+    def view(self, cache_id, step, writes: bool):
+        if cache_id in self.bundles:
+            return BundleView({name: self.view((cache_id, name), step, writes) for name in self.bundles[cache_id]}, writes)
         gname = self.cache_group.get(cache_id)
         if gname is None:
             return None

@@ -36,3 +36,16 @@ class StateLayerView:
     """
     state: torch.Tensor
     writes: bool
+
+
+@dataclass
+class BundleView:
+    """The views of a run that asked for several caches (``CacheBundle``), by the names it gave them."""
+    views: dict
+    writes: bool
+
+    def __getitem__(self, name):
+        return self.views[name]
+
+    def get(self, name, default=None):
+        return self.views.get(name, default)

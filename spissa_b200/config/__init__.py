@@ -3,8 +3,9 @@ from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedul
 from .registry import (UnknownArchitecture, config_class_for, config_from_dict, known_architectures,
                        load_config, register_architecture, unregister_architecture)
 from .llama import ConfigError, LlamaConfig, RopeScaling
+from .duzinex import DuzinexConfig
 
 __all__ = ["LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule",
            "UnknownArchitecture", "config_class_for", "config_from_dict", "known_architectures",
            "load_config", "register_architecture", "unregister_architecture",
-           "ConfigError", "LlamaConfig", "RopeScaling"]
+           "ConfigError", "LlamaConfig", "RopeScaling", "DuzinexConfig"]

@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration class and model.
 
-``config.json`` names the architecture in ``architectures[0]`` (and ``model_type``);
+``config.json`` names the architecture in ``architectures[0]`` (and ``model_type``), or in ``architecture``;
 the reference dispatches on a normalised string
 (crates/spissa-import/src/safetensors.rs:202-232, crates/spissa-cli/src/commands/chat.rs:131-168).
 Here an architecture registers a configuration class with two methods,
@@ -41,6 +41,8 @@ def known_architectures() -> list:
 
 def config_class_for(config_json: dict):
     names = list(config_json.get("architectures") or [])
+    if isinstance(config_json.get("architecture"), str):        # some configurations name one architecture, singular
+        names.append(config_json["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]

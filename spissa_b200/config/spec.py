@@ -29,12 +29,15 @@ class LayerSpec:
     """One layer: an arrangement (``block``) of a mixer, a feed-forward and norms.
 
     ``norms`` maps the arrangement's norm places (for the pre-norm block:
-    ``"mixer"`` and ``"ffn"``) to norm parts.
+    ``"mixer"`` and ``"ffn"``) to norm parts. ``ffn`` None: the layer has no feed-forward
+    (for arrangements that allow it). ``params`` are further constructor keywords of the
+    arrangement itself (sizes and tensor names of what it owns besides its parts).
     """
     block: str
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]
     norms: dict
+    params: dict = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -44,11 +47,14 @@ class ScheduleEntry:
     ``layer`` indexes ``ModelSpec.layers``; a layer may appear in several entries.
     ``cache`` names the cache this run uses: entries with the same ``cache`` share
     it. ``writes_cache`` is False for a run that only reads a cache that an earlier
-    entry of the same step has written.
+    entry of the same step has written. ``adds_embedding``: the embedding's output of
+    the step's tokens is added to the residual stream right before this run (how a group
+    of layers that runs several times takes its input in again at every pass but the first).
     """
     layer: int
     cache: int
     writes_cache: bool = True
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)

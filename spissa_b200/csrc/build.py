@@ -53,6 +53,7 @@ MODULES = {
     "decode_layers": "decode_layers.cu",
     "tc_stream": "tc_stream.cu",
     "host_step": "host_step.cu",
+    "seqmix": "seqmix_kernels.cu",
 }
 
 

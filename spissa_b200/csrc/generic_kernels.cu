@@ -22,26 +22,26 @@ SP_DEFINE_RANGE_API(generic)
 // ============================================================== embedding
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int T, int H, int V, int* status) {
+                                    float* __restrict__ out, int T, int H, int V, int* status, float scale) {
     const int t = blockIdx.x;
     if (t >= T) return;
     const int id = ids[t];
     const bool ok = (id >= 0 && id < V);
     if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0, 301);     // a token id outside the table
     for (int c = threadIdx.x; c < H; c += blockDim.x)
-        out[(size_t)t * H + c] = ok ? sp_ld(table, (size_t)id * H + c) : 0.0f;
+        out[(size_t)t * H + c] = ok ? sp_ld(table, (size_t)id * H + c) * scale : 0.0f;
 }
 
 SP_API int sp_embed_gather(const void* table, int table_dt, const int* ids, float* out,
-                           int T, int H, int V, int* status, cudaStream_t stream) {
+                           int T, int H, int V, int* status, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dt == SP_DT_F32)
         SP_CHECK_CALL("embed_gather", sp_launch_cluster(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, 1,
-                                                   (const float*)table, ids, out, T, H, V, status));
+                                                   (const float*)table, ids, out, T, H, V, status, scale));
     else if (table_dt == SP_DT_BF16)
         SP_CHECK_CALL("embed_gather", sp_launch_cluster(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
-                                                   1, (const __nv_bfloat16*)table, ids, out, T, H, V, status));
+                                                   1, (const __nv_bfloat16*)table, ids, out, T, H, V, status, scale));
     else
         SP_FAIL("embed_gather: unsupported table dtype code %d", table_dt);
     return 0;

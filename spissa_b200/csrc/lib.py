@@ -116,14 +116,14 @@ def _need_contig(*ts):
 
 
 # ------------------------------------------------------------------ generic
-def embed_gather(table, ids, out, status=None):
-    """out[t,:] (float32) = table[ids[t],:]; an id outside the table zeroes the row and sets ``status``."""
+def embed_gather(table, ids, out, status=None, scale: float = 1.0):
+    """out[t,:] (float32) = table[ids[t],:] · scale; an id outside the table zeroes the row and sets ``status``."""
     lib = load("generic")
     T, H = out.shape
     _need_contig(table, ids, out)
     _check("generic", lib.sp_embed_gather(
         c_void_p(_ptr(table)), dt_code(table), c_void_p(_ptr(ids)), c_void_p(_ptr(out)),
-        T, H, table.shape[0], c_void_p(_ptr(status)), c_void_p(_stream())))
+        T, H, table.shape[0], c_void_p(_ptr(status)), c_float(scale), c_void_p(_stream())))
 
 
 def rmsnorm(x, weight, out, eps, rows=None):
@@ -801,3 +801,120 @@ def tc_stream(x, w, out, mode=TC_STORE, pair=0):
     _check("tc_stream", lib.sp_tc_stream(
         c_void_p(_ptr(x)), c_void_p(_ptr(w)), c_void_p(_ptr(out)), dt_code(out), M, N, K, x.stride(0), w.stride(0),
         out.stride(0), int(mode), int(pair), c_void_p(_ptr(status_word(x.device))), c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ seqmix: other mixers, their norm and activation
+def _w_dt(*ts):
+    """The one storage type of a part's small tensors (they come from one checkpoint)."""
+    codes = {dt_code(t) for t in ts if t is not None}
+    if len(codes) != 1:
+        raise KernelError("a part's small tensors must share one storage type")
+    return codes.pop()
+
+
+def dyt_norm(x, weight, bias, alpha, out, rows=None):
+    """out[r,:] = tanh(alpha · x[rows[r] or r,:]) ⊙ weight + bias; ``x`` is the float32 residual stream."""
+    lib = load("seqmix")
+    if x.dtype != torch.float32:
+        raise KernelError("dyt_norm reads the 32-bit residual stream")
+    _need_contig(x, weight, bias, alpha, out, rows)
+    n_rows, H = out.shape
+    _check("seqmix", lib.sp_dyt_norm(
+        c_void_p(_ptr(x)), c_void_p(_ptr(weight)), c_void_p(_ptr(bias)), c_void_p(_ptr(alpha)), _w_dt(weight, bias, alpha),
+        c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(rows)), n_rows, H, c_void_p(_stream())))
+
+
+def token_shift(x, mu, state, out, step, dyt=None):
+    """out[t] = h[t] + (h[t-1] − h[t]) ⊙ mu with h = ``x`` itself, or dyt(x) when ``dyt`` = (weight, bias, alpha) and
+    ``x`` is the float32 residual stream. h[-1] of a step's first token comes from ``state[slot]`` (float32
+    [slots, H]), which then takes the sequence's last h."""
+    lib = load("seqmix")
+    T, H = out.shape
+    _need_contig(x, mu, state, out)
+    if state.dtype != torch.float32 or state.shape[-1] != H:
+        raise KernelError("token_shift keeps a float32 state of the stream's width per slot")
+    w, b, a = dyt if dyt is not None else (None, None, None)
+    global launches
+    if not step.all_single:
+        launches += 1                                  # the state is stored by a second launch behind the first
+    _check("seqmix", lib.sp_token_shift(
+        c_void_p(_ptr(x)), dt_code(x), c_void_p(_ptr(w)), c_void_p(_ptr(b)), c_void_p(_ptr(a)),
+        _w_dt(w, b, a) if dyt is not None else 0, c_void_p(_ptr(mu)), dt_code(mu), c_void_p(_ptr(state)), state.shape[0],
+        c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.token_seq)), c_void_p(_ptr(step.seq_start)),
+        c_void_p(_ptr(step.seq_slot)), T, step.n_seqs, H, int(bool(step.all_single)), c_void_p(_stream())))
+
+
+def diff_qkv_store(qkv, bias, q_out, k_pool, v_pool, meta, inv_freq, nq, nk, G, d, vd, rd):
+    """Add ``bias``, rotate neighbouring pairs over the first ``rd`` dims of each of the nq + nk sub-heads of size d,
+    store q to ``q_out`` and k (rows of nk/G·d per kv head) and v (rows of vd) into the paged cache."""
+    lib = load("seqmix")
+    if qkv.dtype != torch.float32:
+        raise KernelError("diff_qkv_store reads 32-bit projections")
+    _need_contig(qkv, bias, q_out)
+    T = qkv.shape[0]
+    pt = meta.page_table
+    _declare_bounds("seqmix", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), qkv.device)
+    _check("seqmix", lib.sp_diff_qkv_store(
+        c_void_p(_ptr(qkv)), c_void_p(_ptr(bias)), dt_code(bias) if bias is not None else 0, c_void_p(_ptr(q_out)),
+        dt_code(q_out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool), c_void_p(_ptr(meta.token_seq)),
+        c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
+        c_void_p(_ptr(inv_freq)), T, nq, nk, G, d, vd, rd, c_void_p(_stream())))
+
+
+def diff_attention(q, k_pool, v_pool, out, meta, H, G, d, vd, window, keep_first, scale, softcap, lam, eps, out_scale):
+    """Two softmax maps per head over one set of values, a1 − lam·a2, unit rms per head, times ``out_scale``."""
+    lib = load("seqmix")
+    _need_contig(q, out)
+    T = q.shape[0]
+    pt = meta.page_table
+    _declare_bounds("seqmix", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
+    _check("seqmix", lib.sp_diff_attention(
+        c_void_p(_ptr(q)), dt_code(q), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool), c_void_p(_ptr(out)),
+        c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)),
+        pt.shape[1], meta.page_size, T, H, G, d, vd, int(window or 0), int(keep_first or 0), c_float(scale),
+        c_float(softcap or 0.0), c_float(lam), c_float(eps), c_float(out_scale), c_void_p(_stream())))
+
+
+def retention(proj, state, decay, out, step, H, d, vd, eps):
+    """proj rows [q | k | v | g] (float32); state float32 [slots, H, d, vd]; out [T, H·vd]."""
+    lib = load("seqmix")
+    if proj.dtype != torch.float32 or state.dtype != torch.float32 or decay.dtype != torch.float32:
+        raise KernelError("retention runs on 32-bit projections, state and decays")
+    _need_contig(proj, state, decay, out)
+    _check("seqmix", lib.sp_retention(
+        c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(decay)),
+        c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), step.n_seqs,
+        H, d, vd, c_float(eps), c_void_p(_stream())))
+
+
+def mingru(proj, z_bias, x_bias, state, out, step, W):
+    """proj rows [z | x | g] (float32, biases not yet added); state float32 [slots, W]; out [T, W]."""
+    lib = load("seqmix")
+    if proj.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("mingru runs on 32-bit projections and state")
+    _need_contig(proj, z_bias, x_bias, state, out)
+    _check("seqmix", lib.sp_mingru(
+        c_void_p(_ptr(proj)), c_void_p(_ptr(z_bias)), c_void_p(_ptr(x_bias)), _w_dt(z_bias, x_bias), c_void_p(_ptr(state)),
+        state.shape[0], c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)),
+        step.n_seqs, W, c_void_p(_stream())))
+
+
+def polynorm(z, coef, out, eps):
+    """out = a·N(z) + b·N(z²) + c·N(z³) + e per row of ``z`` (float32), (a, b, c, e) = ``coef``."""
+    lib = load("seqmix")
+    if z.dtype != torch.float32:
+        raise KernelError("polynorm reads 32-bit pre-activations")
+    _need_contig(z, coef, out)
+    T, F = z.shape
+    _check("seqmix", lib.sp_polynorm(c_void_p(_ptr(z)), c_void_p(_ptr(coef)), dt_code(coef), c_void_p(_ptr(out)),
+                                     dt_code(out), T, F, c_float(eps), c_void_p(_stream())))
+
+
+def add_bias(x, bias):
+    """Every row of ``x`` (float32 [T, N]) += ``bias`` [N]."""
+    lib = load("seqmix")
+    if x.dtype != torch.float32 or bias.numel() != x.shape[1]:
+        raise KernelError("add_bias wants a float32 matrix and one bias per column")
+    _need_contig(x, bias)
+    _check("seqmix", lib.sp_add_bias(c_void_p(_ptr(x)), c_void_p(_ptr(bias)), dt_code(bias), x.shape[0], x.shape[1],
+                                     c_void_p(_stream())))

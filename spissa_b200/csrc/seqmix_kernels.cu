@@ -1,0 +1,565 @@
+// Sequence mixers beyond softmax attention over one map, with the small kernels that surround them.
+//
+//   dyt_norm          y = tanh(alpha·x) ⊙ w + b                 (a norm without statistics)
+//   token_shift       h_t ← h_t + (h_{t-1} − h_t) ⊙ mu          (h_{-1} = 0; the last h is a sequence's state)
+//   diff_qkv_store    bias, rotation of interleaved pairs on the first dims of every sub-head, q out, k / v to pages
+//   diff_attention    two softmax maps per head over one set of values, combined as a1 − λ·a2, unit rms per head;
+//                     scores capped by c·tanh(s/c); a sliding window that also keeps the first tokens
+//   retention         S_t = γ_h S_{t-1} + k_t v_tᵀ, o_t = S_tᵀ q_t, unit rms per head, gate silu(g)
+//   mingru            S_t = (1 − z_t) S_{t-1} + z_t c_t element by element, gate silu(g)
+//   polynorm          a·N(z) + b·N(z²) + c·N(z³) + e with N(v) = v / rms(v) over a token's row
+//   add_bias          rows of a 32-bit matrix += a vector
+//
+// Everything here is computed in 32-bit from 32-bit projections (FFMA, expf / tanhf / sqrtf / division without
+// fast-math); only the stores round to the activation type. States are 32-bit. Every output row is reduced in an
+// order that depends on its own sequence only, never on the batch or on how the tokens were cut into steps beyond
+// the point where a step begins (a recurrence restarts from the stored state, which is exact).
+#include "common.cuh"
+
+SP_API const char* sp_seqmix_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(seqmix)
+
+__device__ __forceinline__ float sm_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sm_silu(float x) { return x / (1.0f + expf(-x)); }
+
+// ============================================================== dynamic tanh norm
+// One block per output row; ``rows`` (optional) gathers input rows.
+__global__ void dyt_norm_kernel(const float* __restrict__ x, const void* __restrict__ w, const void* __restrict__ b,
+                                const void* __restrict__ alpha, int w_dt, void* __restrict__ out, int out_dt,
+                                const int* __restrict__ rows, int n_rows, int H) {
+    const int r = blockIdx.x;
+    if (r >= n_rows) return;
+    const float a = sp_ld_dt(alpha, w_dt, 0);
+    const size_t src = (size_t)(rows ? rows[r] : r) * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        sp_st_dt(out, out_dt, (size_t)r * H + c, tanhf(a * x[src + c]) * sp_ld_dt(w, w_dt, c) + sp_ld_dt(b, w_dt, c));
+}
+
+SP_API int sp_dyt_norm(const float* x, const void* w, const void* b, const void* alpha, int w_dt, void* out, int out_dt,
+                       const int* rows, int n_rows, int H, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    dyt_norm_kernel<<<n_rows, H >= 1024 ? 256 : 128, 0, stream>>>(x, w, b, alpha, w_dt, out, out_dt, rows, n_rows, H);
+    SP_CHECK_LAUNCH("dyt_norm");
+    return 0;
+}
+
+// ============================================================== token shift (with the norm in front of it, if it is dyt)
+// DYT: ``x`` is the 32-bit residual stream and h = dyt(x); else ``x`` holds h itself in ``x_dt``.
+// A token that is the first of its sequence in this step takes h_{t-1} from state[slot] (zero for a new sequence).
+// ``save``: 1 = the block of a sequence's last token also stores its h as the new state. That is only safe when no
+// other block reads that row, i.e. when every sequence brings one token; otherwise the host launches the save kernel
+// behind this one.
+struct ShiftArgs {
+    const void* x; int x_dt;
+    const void* w; const void* b; const void* alpha; int w_dt;      // dyt (unused when !DYT)
+    const void* mu; int mu_dt;
+    float* state;                                                    // [slots][H]
+    void* out; int out_dt;
+    const int* token_seq; const int* seq_start; const int* seq_slot;
+    int T, H, n_slots;
+};
+
+template <bool DYT>
+__device__ __forceinline__ float shift_h(const ShiftArgs& a, size_t row, int c, float alpha) {
+    if (DYT) return tanhf(alpha * ((const float*)a.x)[row * a.H + c]) * sp_ld_dt(a.w, a.w_dt, c) + sp_ld_dt(a.b, a.w_dt, c);
+    return sp_ld_dt(a.x, a.x_dt, row * a.H + c);
+}
+
+template <bool DYT>
+__global__ void token_shift_kernel(ShiftArgs a, int save) {
+    const int t = blockIdx.x;
+    if (t >= a.T) return;
+    const int s = a.token_seq[t];
+    const bool first = t == a.seq_start[s], last = t + 1 == a.seq_start[s + 1];
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const float alpha = DYT ? sp_ld_dt(a.alpha, a.w_dt, 0) : 0.0f;
+    float* st = a.state + (size_t)slot * a.H;
+    for (int c = threadIdx.x; c < a.H; c += blockDim.x) {
+        const float h = shift_h<DYT>(a, t, c, alpha);
+        const float prev = first ? st[c] : shift_h<DYT>(a, t - 1, c, alpha);
+        sp_st_dt(a.out, a.out_dt, (size_t)t * a.H + c, h + (prev - h) * sp_ld_dt(a.mu, a.mu_dt, c));
+        if (save && last) st[c] = h;
+    }
+}
+
+template <bool DYT>
+__global__ void token_shift_save_kernel(ShiftArgs a, int B) {
+    const int s = blockIdx.x;
+    if (s >= B) return;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int t = a.seq_start[s + 1] - 1;
+    if (t < a.seq_start[s]) return;
+    const float alpha = DYT ? sp_ld_dt(a.alpha, a.w_dt, 0) : 0.0f;
+    for (int c = threadIdx.x; c < a.H; c += blockDim.x) a.state[(size_t)slot * a.H + c] = shift_h<DYT>(a, t, c, alpha);
+}
+
+SP_API int sp_token_shift(const void* x, int x_dt, const void* w, const void* b, const void* alpha, int w_dt,
+                          const void* mu, int mu_dt, float* state, int n_slots, void* out, int out_dt,
+                          const int* token_seq, const int* seq_start, const int* seq_slot, int T, int B, int H,
+                          int all_single, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const bool dyt = w != nullptr;
+    if (dyt && x_dt != SP_DT_F32) SP_FAIL("token_shift: the norm reads the 32-bit residual stream");
+    ShiftArgs a{x, x_dt, w, b, alpha, w_dt, mu, mu_dt, state, out, out_dt, token_seq, seq_start, seq_slot, T, H, n_slots};
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dyt) token_shift_kernel<true><<<T, threads, 0, stream>>>(a, all_single);
+    else token_shift_kernel<false><<<T, threads, 0, stream>>>(a, all_single);
+    SP_CHECK_LAUNCH("token_shift");
+    if (!all_single) {
+        if (dyt) token_shift_save_kernel<true><<<B, threads, 0, stream>>>(a, B);
+        else token_shift_save_kernel<false><<<B, threads, 0, stream>>>(a, B);
+        SP_CHECK_LAUNCH("token_shift_save");
+    }
+    return 0;
+}
+
+// ============================================================== where a token's keys and values live
+struct KvPlace {
+    const int* token_seq;     // [T] sequence index of each token
+    const int* positions;     // [T] absolute position of each token
+    const int* seq_slot;      // [B] row of each sequence in the page table
+    const int* page_table;    // [rows][max_pages]
+    int max_pages;
+    int page_size;
+    SpRange rg;
+};
+
+__device__ __forceinline__ bool kv_page_of(const KvPlace& pl, int t, int pos, int& page) {
+    const int row = pl.seq_slot[pl.token_seq[t]];
+    if (!sp_index_ok(row, pl.rg.n_rows, pl.rg, 402) || !sp_index_ok(pos / pl.page_size, pl.max_pages, pl.rg, 403)) return false;
+    page = pl.page_table[(size_t)row * pl.max_pages + pos / pl.page_size];
+    return sp_index_ok(page, pl.rg.n_pages, pl.rg, 401);
+}
+
+// ============================================================== bias + rotation of interleaved pairs + cache write
+// A row of ``qkv`` (32-bit) is [nq sub-heads of d | nk sub-heads of d | G value heads of vd]. A sub-head is one
+// map of one head; the first ``rd`` dims of each are rotated, dim 2i with dim 2i+1 by the angle position·inv_freq[i].
+// q goes to ``q_out`` [T][nq·d]; the k sub-heads of kv head g are the contiguous row of 2·d (nk/G · d) numbers that
+// the key pool holds for the token, [page][G][page_size][nk/G·d]; v likewise with rows of vd.
+template <typename TO, typename TC>
+__global__ void diff_qkv_store_kernel(const float* __restrict__ qkv, const void* __restrict__ bias, int b_dt,
+                                      TO* __restrict__ q_out, TC* __restrict__ kpool, TC* __restrict__ vpool, KvPlace pl,
+                                      const float* __restrict__ inv_freq, int T, int nq, int nk, int G, int d, int vd,
+                                      int rd) {
+    extern __shared__ float cs[];                  // [2][rd/2]
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const int pos = pl.positions[t];
+    const int half = rd >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * inv_freq[i];
+        cs[i] = cosf(ang);
+        cs[half + i] = sinf(ang);
+    }
+    __syncthreads();
+    int page = 0;
+    const bool place_ok = kv_page_of(pl, t, pos, page);
+    const int off = pos % pl.page_size;
+    const int row = (nq + nk) * d + G * vd;
+    const float* src = qkv + (size_t)t * row;
+    const int dp = d >> 1;                          // pairs per sub-head (d is even)
+    const int kd = (nk / G) * d;                    // a key row of one kv head
+    for (int e = threadIdx.x; e < (nq + nk) * dp; e += blockDim.x) {
+        const int sh = e / dp, i = e - sh * dp;
+        const int c = sh * d + 2 * i;
+        float u = src[c], v = src[c + 1];
+        if (bias) { u += sp_ld_dt(bias, b_dt, c); v += sp_ld_dt(bias, b_dt, c + 1); }
+        if (2 * i < rd) {
+            const float co = cs[i], si = cs[half + i];
+            const float ru = u * co - v * si, rv = v * co + u * si;
+            u = ru; v = rv;
+        }
+        if (sh < nq) {
+            sp_st2(q_out, (size_t)t * nq * d + c, u, v);
+        } else if (place_ok) {
+            const int ck = c - nq * d;              // column within the token's key numbers
+            const int g = ck / kd, r = ck - g * kd;
+            sp_st2(kpool, (((size_t)page * G + g) * pl.page_size + off) * kd + r, u, v);
+        }
+    }
+    if (place_ok) {
+        for (int e = threadIdx.x; e < G * vd; e += blockDim.x) {
+            const int g = e / vd, r = e - g * vd;
+            float v = src[(nq + nk) * d + e];
+            if (bias) v += sp_ld_dt(bias, b_dt, (nq + nk) * d + e);
+            sp_st(vpool, (((size_t)page * G + g) * pl.page_size + off) * vd + r, v);
+        }
+    }
+}
+
+SP_API int sp_diff_qkv_store(const float* qkv, const void* bias, int b_dt, void* q_out, int q_dt, void* kpool, void* vpool,
+                             int cache_dt, const int* token_seq, const int* positions, const int* seq_slot,
+                             const int* page_table, int max_pages, int page_size, const float* inv_freq, int T, int nq,
+                             int nk, int G, int d, int vd, int rd, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || (d & 1) || rd < 0 || rd > d || (rd & 1)) SP_FAIL("qkv_store: sizes d %d, rotated %d must be even, rotated <= d", d, rd);
+    if (G <= 0 || nk % G) SP_FAIL("qkv_store: %d key sub-heads are no multiple of %d kv heads", nk, G);
+    if (rd > 0 && !inv_freq) SP_FAIL("qkv_store: a frequency table is needed");
+    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
+    const size_t smem = (size_t)rd * sizeof(float);
+#define QS_LAUNCH(TO, TC)                                                                                          \
+    diff_qkv_store_kernel<TO, TC><<<T, 128, smem, stream>>>(qkv, bias, b_dt, (TO*)q_out, (TC*)kpool, (TC*)vpool, pl, \
+                                                           inv_freq, T, nq, nk, G, d, vd, rd)
+    if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) QS_LAUNCH(float, float);
+    else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) QS_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) QS_LAUNCH(float, __nv_bfloat16);
+    else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_F32) QS_LAUNCH(__nv_bfloat16, float);
+    else SP_FAIL("qkv_store: unsupported dtype codes %d/%d", q_dt, cache_dt);
+#undef QS_LAUNCH
+    SP_CHECK_LAUNCH("diff_qkv_store");
+    return 0;
+}
+
+// ============================================================== differential attention over the cache
+// One warp per (token, head), both maps at once: lane j scores key j against the head's two query halves, two online
+// softmaxes run side by side in 32-bit, and every value row is fetched once for both. A query at position p sees the
+// keys max(0, p−window+1) … p (all keys when window = 0) and, before them, the keys 0 … keep_first−1; the visible keys are
+// walked as one list, kept ones first. SPLIT: the four warps of a CTA share one (token, head) and take chunks of 32
+// keys in turn; warp 0 merges their parts in warp order.
+#define DA_WARPS 4
+#define DA_MAX_D 128           // per-map query/key size
+#define DA_MAX_VD 256          // value size
+
+struct DiffArgs {
+    int T, H, G, d, vd, window, keep_first;
+    float scale, softcap, lam, eps, out_scale;
+};
+
+template <typename TQ, typename TC, bool SPLIT>
+__global__ void __launch_bounds__(DA_WARPS * 32)
+diff_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
+                      TQ* __restrict__ out, KvPlace pl, DiffArgs a) {
+    __shared__ __align__(16) float qs[DA_WARPS][2 * DA_MAX_D];
+    __shared__ float part[SPLIT ? DA_WARPS : 1][2][SPLIT ? DA_MAX_VD : 1];
+    __shared__ float part_ml[DA_WARPS][4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long gw = SPLIT ? (long long)blockIdx.x : (long long)blockIdx.x * DA_WARPS + warp;
+    if (gw >= (long long)a.T * a.H) return;
+    const int t = (int)(gw / a.H), h = (int)(gw % a.H);
+    const int g = h / (a.H / a.G);
+    const int d = a.d, vd = a.vd, kd = 2 * a.d;
+    const int p = pl.positions[t];
+    const int row = sp_checked_row(pl.seq_slot[pl.token_seq[t]], pl.rg);
+    const int* pt = pl.page_table + (size_t)row * pl.max_pages;
+    const int ps = pl.page_size;
+
+    for (int c = lane; c < kd; c += 32) qs[warp][c] = sp_ld(q, ((size_t)t * a.H + h) * kd + c);
+    __syncwarp();
+
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    const int n_first = a.keep_first < lo ? a.keep_first : lo;       // kept keys that lie before the window
+    const int n_vis = n_first + (p - lo + 1);
+    float m1 = -INFINITY, l1 = 0.0f, m2 = -INFINITY, l2 = 0.0f;
+    float acc1[DA_MAX_VD / 32], acc2[DA_MAX_VD / 32];
+#pragma unroll
+    for (int i = 0; i < DA_MAX_VD / 32; ++i) acc1[i] = acc2[i] = 0.0f;
+
+    for (int v0 = SPLIT ? 32 * warp : 0; v0 < n_vis; v0 += SPLIT ? 32 * DA_WARPS : 32) {
+        const int vi = v0 + lane;
+        const bool valid = vi < n_vis;
+        float s1 = -INFINITY, s2 = -INFINITY;
+        int my_page = 0, my_off = 0;
+        if (valid) {
+            const int j = vi < n_first ? vi : lo + (vi - n_first);
+            my_page = sp_checked_page(pt[sp_checked_entry(j / ps, pl.max_pages, pl.rg)], pl.rg);
+            my_off = j % ps;
+            const TC* kr = kpool + (((size_t)my_page * a.G + g) * ps + my_off) * kd;
+            float d1 = 0.0f, d2 = 0.0f;
+            for (int c = 0; c < d; ++c) {
+                d1 = fmaf(qs[warp][c], sp_ld(kr, c), d1);
+                d2 = fmaf(qs[warp][d + c], sp_ld(kr, d + c), d2);
+            }
+            s1 = d1 * a.scale;
+            s2 = d2 * a.scale;
+            if (a.softcap > 0.0f) {
+                s1 = a.softcap * tanhf(s1 / a.softcap);
+                s2 = a.softcap * tanhf(s2 / a.softcap);
+            }
+        }
+        const float n1 = fmaxf(m1, sp_warp_max(s1)), n2 = fmaxf(m2, sp_warp_max(s2));
+        const float e1 = valid ? expf(s1 - n1) : 0.0f, e2 = valid ? expf(s2 - n2) : 0.0f;
+        const float c1 = expf(m1 - n1), c2 = expf(m2 - n2);            // first chunk: exp(-inf) = 0
+        l1 = l1 * c1 + sp_warp_sum(e1);
+        l2 = l2 * c2 + sp_warp_sum(e2);
+#pragma unroll
+        for (int i = 0; i < DA_MAX_VD / 32; ++i) { acc1[i] *= c1; acc2[i] *= c2; }
+        const int n_valid = min(32, n_vis - v0);
+        for (int jj0 = 0; jj0 < n_valid; jj0 += 4) {
+            float w1[4], w2[4];
+            const TC* vr[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                w1[u] = __shfl_sync(0xffffffffu, e1, jj0 + u);
+                w2[u] = __shfl_sync(0xffffffffu, e2, jj0 + u);
+                const int pg = __shfl_sync(0xffffffffu, my_page, jj0 + u);
+                const int of = __shfl_sync(0xffffffffu, my_off, jj0 + u);
+                vr[u] = vpool + (((size_t)pg * a.G + g) * ps + of) * vd;
+            }
+#pragma unroll
+            for (int i = 0; i < DA_MAX_VD / 32; ++i) {
+                const int c = lane + 32 * i;
+                if (c < vd) {
+                    float v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[u] = jj0 + u < n_valid ? sp_ld(vr[u], c) : 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { acc1[i] = fmaf(w1[u], v[u], acc1[i]); acc2[i] = fmaf(w2[u], v[u], acc2[i]); }
+                }
+            }
+        }
+        m1 = n1;
+        m2 = n2;
+    }
+    if (SPLIT) {
+#pragma unroll
+        for (int i = 0; i < DA_MAX_VD / 32; ++i) {
+            const int c = lane + 32 * i;
+            if (c < vd) { part[warp][0][c] = acc1[i]; part[warp][1][c] = acc2[i]; }
+        }
+        if (lane == 0) { part_ml[warp][0] = m1; part_ml[warp][1] = l1; part_ml[warp][2] = m2; part_ml[warp][3] = l2; }
+        __syncthreads();
+        if (warp != 0) return;
+        float mm1 = -INFINITY, mm2 = -INFINITY;
+        for (int w = 0; w < DA_WARPS; ++w) { mm1 = fmaxf(mm1, part_ml[w][0]); mm2 = fmaxf(mm2, part_ml[w][2]); }
+        l1 = l2 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DA_MAX_VD / 32; ++i) acc1[i] = acc2[i] = 0.0f;
+        for (int w = 0; w < DA_WARPS; ++w) {
+            if (part_ml[w][1] <= 0.0f) continue;                     // a warp that saw no key
+            const float f1 = expf(part_ml[w][0] - mm1), f2 = expf(part_ml[w][2] - mm2);
+            l1 += part_ml[w][1] * f1;
+            l2 += part_ml[w][3] * f2;
+#pragma unroll
+            for (int i = 0; i < DA_MAX_VD / 32; ++i) {
+                const int c = lane + 32 * i;
+                if (c < vd) { acc1[i] = fmaf(part[w][0][c], f1, acc1[i]); acc2[i] = fmaf(part[w][1][c], f2, acc2[i]); }
+            }
+        }
+    }
+    // o = a1 − λ·a2, then unit rms over the head's values, then the constant factor
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < DA_MAX_VD / 32; ++i) {
+        const int c = lane + 32 * i;
+        if (c < vd) {
+            acc1[i] = acc1[i] / l1 - a.lam * (acc2[i] / l2);
+            ss = fmaf(acc1[i], acc1[i], ss);
+        }
+    }
+    ss = sp_warp_sum(ss);
+    const float inv = a.out_scale / sqrtf(ss / (float)vd + a.eps);
+#pragma unroll
+    for (int i = 0; i < DA_MAX_VD / 32; ++i) {
+        const int c = lane + 32 * i;
+        if (c < vd) sp_st(out, ((size_t)t * a.H + h) * vd + c, acc1[i] * inv);
+    }
+}
+
+SP_API int sp_diff_attention(const void* q, int q_dt, const void* kpool, const void* vpool, int cache_dt, void* out,
+                             const int* token_seq, const int* positions, const int* seq_slot, const int* page_table,
+                             int max_pages, int page_size, int T, int H, int G, int d, int vd, int window, int keep_first,
+                             float scale, float softcap, float lam, float eps, float out_scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || d > DA_MAX_D) SP_FAIL("diff_attention: map size %d is beyond this kernel's limit %d", d, DA_MAX_D);
+    if (vd <= 0 || vd > DA_MAX_VD) SP_FAIL("diff_attention: value size %d is beyond this kernel's limit %d", vd, DA_MAX_VD);
+    if (G <= 0 || H % G) SP_FAIL("diff_attention: %d heads are no multiple of %d kv heads", H, G);
+    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
+    DiffArgs a{T, H, G, d, vd, window, keep_first < 0 ? 0 : keep_first, scale, softcap, lam, eps, out_scale};
+    const long long warps = (long long)T * H;
+    const bool split = warps <= 2048;
+    const long long blocks = split ? warps : (warps + DA_WARPS - 1) / DA_WARPS;
+    if (blocks > 2147483647LL) SP_FAIL("diff_attention: too many (token, head) pairs for one launch");
+#define DA_LAUNCH(TQ, TC)                                                                                             \
+    do {                                                                                                              \
+        if (split) diff_attention_kernel<TQ, TC, true><<<(unsigned)blocks, DA_WARPS * 32, 0, stream>>>(               \
+                (const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, a);                                   \
+        else diff_attention_kernel<TQ, TC, false><<<(unsigned)blocks, DA_WARPS * 32, 0, stream>>>(                    \
+                (const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, a);                                   \
+    } while (0)
+    if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) DA_LAUNCH(float, float);
+    else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) DA_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) DA_LAUNCH(float, __nv_bfloat16);
+    else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_F32) DA_LAUNCH(__nv_bfloat16, float);
+    else SP_FAIL("diff_attention: unsupported dtype codes %d/%d", q_dt, cache_dt);
+#undef DA_LAUNCH
+    SP_CHECK_LAUNCH("diff_attention");
+    return 0;
+}
+
+// ============================================================== retention, token by token
+// proj row (32-bit) = [q: H·d | k: H·d | v: H·vd | g: H·vd]. One CTA per (sequence, head): the state S [d][vd] lives in
+// shared memory for the whole step; thread (j, y) owns column j of the rows i ≡ y (mod DY). Per token:
+// S ← γ S + (k/√d) vᵀ, o_j = Σ_i S_ij q_i (the DY partial sums added in the order of y), o / rms(o) ⊙ silu(g).
+struct RetArgs {
+    const float* proj; int ld;
+    float* state;                      // [slots][H][d][vd]
+    const float* decay;                // [H]
+    void* out; int out_dt;             // [T][H·vd]
+    const int* seq_start; const int* seq_slot;
+    int B, H, d, vd, n_slots;
+    float eps;
+};
+
+__global__ void retention_scan_kernel(RetArgs a, int vdr, int DY) {
+    extern __shared__ float sm[];
+    const int d = a.d, vd = a.vd;
+    float* S = sm;                         // [d][vd]
+    float* qk = S + (size_t)d * vd;        // q [d], k [d]
+    float* red = qk + 2 * d;               // [DY][vdr]
+    float* o = red + (size_t)DY * vdr;     // [vdr]
+    __shared__ float inv_rms;
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int j = threadIdx.x % vdr, y = threadIdx.x / vdr;
+    float* gS = a.state + ((size_t)slot * a.H + h) * d * vd;
+    for (int e = threadIdx.x; e < d * vd; e += blockDim.x) S[e] = gS[e];
+    const float gamma = a.decay[h];
+    const float kscale = 1.0f / sqrtf((float)d);
+    const int Hd = a.H * d, Hv = a.H * vd;
+    for (int t = a.seq_start[s]; t < a.seq_start[s + 1]; ++t) {
+        const float* row = a.proj + (size_t)t * a.ld;
+        __syncthreads();
+        for (int e = threadIdx.x; e < d; e += blockDim.x) {
+            qk[e] = row[h * d + e];
+            qk[d + e] = row[Hd + h * d + e] * kscale;
+        }
+        __syncthreads();
+        float part = 0.0f;
+        if (j < vd) {
+            const float v = row[2 * Hd + h * vd + j];
+            for (int i = y; i < d; i += DY) {
+                const float sv = fmaf(gamma, S[i * vd + j], qk[d + i] * v);
+                S[i * vd + j] = sv;
+                part = fmaf(sv, qk[i], part);
+            }
+        }
+        red[y * vdr + j] = part;
+        __syncthreads();
+        if (y == 0) {
+            float sum = 0.0f;
+            for (int yy = 0; yy < DY; ++yy) sum += red[yy * vdr + j];
+            o[j] = j < vd ? sum : 0.0f;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float ss = 0.0f;
+            for (int c = threadIdx.x; c < vd; c += 32) ss = fmaf(o[c], o[c], ss);
+            ss = sp_warp_sum(ss);
+            if (threadIdx.x == 0) inv_rms = 1.0f / sqrtf(ss / (float)vd + a.eps);
+        }
+        __syncthreads();
+        if (y == 0 && j < vd)
+            sp_st_dt(a.out, a.out_dt, (size_t)t * Hv + h * vd + j, o[j] * inv_rms * sm_silu(row[2 * Hd + Hv + h * vd + j]));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < d * vd; e += blockDim.x) gS[e] = S[e];
+}
+
+static SpPerDevice retention_ready;
+
+SP_API int sp_retention(const float* proj, int ld, float* state, int n_slots, const float* decay, void* out, int out_dt,
+                        const int* seq_start, const int* seq_slot, int B, int H, int d, int vd, float eps,
+                        cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (d <= 0 || vd <= 0 || vd > 1024) SP_FAIL("retention: sizes d %d, vd %d are outside this kernel's range", d, vd);
+    const int vdr = (vd + 31) / 32 * 32;
+    int DY = 256 / vdr;
+    if (DY < 1) DY = 1;
+    if (DY > d) DY = d;
+    const size_t smem = ((size_t)d * vd + 2 * d + (size_t)DY * vdr + vdr) * sizeof(float);
+    if (smem > 220 * 1024) SP_FAIL("retention: a state of %d x %d does not fit shared memory", d, vd);
+    if (!retention_ready.done()) {
+        if (cudaFuncSetAttribute(retention_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess)
+            SP_FAIL("retention: cannot raise the shared memory limit");
+        retention_ready.mark();
+    }
+    RetArgs a{proj, ld, state, decay, out, out_dt, seq_start, seq_slot, B, H, d, vd, n_slots, eps};
+    retention_scan_kernel<<<dim3(B, H), vdr * DY, smem, stream>>>(a, vdr, DY);
+    SP_CHECK_LAUNCH("retention");
+    return 0;
+}
+
+// ============================================================== minGRU, token by token
+// proj row (32-bit) = [z: W | x: W | g: W] without the biases. One thread per (sequence, channel).
+__global__ void mingru_scan_kernel(const float* __restrict__ proj, const void* __restrict__ zb, const void* __restrict__ xb,
+                                   int b_dt, float* __restrict__ state, int n_slots, void* __restrict__ out, int out_dt,
+                                   const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int B, int W) {
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= B || c >= W) return;
+    const int slot = seq_slot[s];
+    if (slot < 0 || slot >= n_slots) return;
+    const float bz = sp_ld_dt(zb, b_dt, c), bx = sp_ld_dt(xb, b_dt, c);
+    float S = state[(size_t)slot * W + c];
+    for (int t = seq_start[s]; t < seq_start[s + 1]; ++t) {
+        const float* row = proj + (size_t)t * 3 * W;
+        const float z = sm_sigmoid(row[c] + bz);
+        const float u = row[W + c] + bx;
+        const float cand = u >= 0.0f ? u + 0.5f : sm_sigmoid(u);
+        S = (1.0f - z) * S + z * cand;
+        sp_st_dt(out, out_dt, (size_t)t * W + c, S * sm_silu(row[2 * W + c]));
+    }
+    state[(size_t)slot * W + c] = S;
+}
+
+SP_API int sp_mingru(const float* proj, const void* zb, const void* xb, int b_dt, float* state, int n_slots, void* out,
+                     int out_dt, const int* seq_start, const int* seq_slot, int B, int W, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    const int threads = 128;
+    mingru_scan_kernel<<<dim3((W + threads - 1) / threads, B), threads, 0, stream>>>(proj, zb, xb, b_dt, state, n_slots, out,
+                                                                                    out_dt, seq_start, seq_slot, B, W);
+    SP_CHECK_LAUNCH("mingru");
+    return 0;
+}
+
+// ============================================================== PolyNorm
+// out = a·z/rms(z) + b·z²/rms(z²) + c·z³/rms(z³) + e over each row of z (32-bit), rms with eps inside the root.
+__global__ void __launch_bounds__(256)
+polynorm_kernel(const float* __restrict__ z, const void* __restrict__ coef, int c_dt, void* __restrict__ out, int out_dt,
+                int T, int F, float eps) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const float* row = z + (size_t)t * F;
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+        const float v = row[c], v2 = v * v, v3 = v2 * v;
+        s2 = fmaf(v, v, s2);
+        s4 = fmaf(v2, v2, s4);
+        s6 = fmaf(v3, v3, s6);
+    }
+    s2 = sp_block_sum(s2, scratch);
+    s4 = sp_block_sum(s4, scratch);
+    s6 = sp_block_sum(s6, scratch);
+    const float r1 = 1.0f / sqrtf(s2 / (float)F + eps), r2 = 1.0f / sqrtf(s4 / (float)F + eps), r3 = 1.0f / sqrtf(s6 / (float)F + eps);
+    const float ca = sp_ld_dt(coef, c_dt, 0), cb = sp_ld_dt(coef, c_dt, 1), cc = sp_ld_dt(coef, c_dt, 2), ce = sp_ld_dt(coef, c_dt, 3);
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+        const float v = row[c], v2 = v * v, v3 = v2 * v;
+        sp_st_dt(out, out_dt, (size_t)t * F + c, ca * (v * r1) + cb * (v2 * r2) + cc * (v3 * r3) + ce);
+    }
+}
+
+SP_API int sp_polynorm(const float* z, const void* coef, int c_dt, void* out, int out_dt, int T, int F, float eps,
+                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    polynorm_kernel<<<T, 256, 0, stream>>>(z, coef, c_dt, out, out_dt, T, F, eps);
+    SP_CHECK_LAUNCH("polynorm");
+    return 0;
+}
+
+// ============================================================== rows += bias
+__global__ void add_bias_kernel(float* __restrict__ x, const void* __restrict__ bias, int b_dt, size_t n, int N) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += sp_ld_dt(bias, b_dt, i % N);
+}
+
+SP_API int sp_add_bias(float* x, const void* bias, int b_dt, int T, int N, cudaStream_t stream) {
+    const size_t n = (size_t)T * N;
+    if (n == 0) return 0;
+    add_bias_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, bias, b_dt, n, N);
+    SP_CHECK_LAUNCH("add_bias");
+    return 0;
+}

@@ -50,7 +50,7 @@ def collect_fused_fields(model):
     fields = []
     for e in model.spec.schedule:
         blk = model.layers[e.layer]
-        f = blk.fused_fields() if e.writes_cache else None
+        f = blk.fused_fields() if e.writes_cache and not e.adds_embedding else None
         if not f or f.get("kind") != "prenorm" or f["mixer"].get("kind") != "gqa_rotary" \
                 or f["ffn"].get("kind") != "swiglu" or f["mixer_norm"].get("kind") != "rmsnorm" \
                 or f["ffn_norm"].get("kind") != "rmsnorm":

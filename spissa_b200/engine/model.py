@@ -14,6 +14,7 @@ from ..parts import registry as part_registry
 from ..parts.base import Runtime
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
 from ..phases import phase, profiling
+from ..csrc import lib as K
 
 
 class Model:
@@ -28,7 +29,7 @@ class Model:
             except KeyError:
                 raise ValueError(f"no block arrangement registered as {layer.block!r}; "
                                  f"known: {part_registry.known_parts('block')}") from None
-            self.layers.append(cls(mixer=layer.mixer, ffn=layer.ffn, norms=layer.norms))
+            self.layers.append(cls(mixer=layer.mixer, ffn=layer.ffn, norms=layer.norms, **layer.params))
         self.final_norm = part_registry.build_part("norm", spec.final_norm)
         self.head = part_registry.build_part("head", spec.head)
         self.rt = None
@@ -42,10 +43,22 @@ class Model:
     def kernel_modules(self, act_dtype) -> list:
         """The kernel libraries that steps of this model can need, for building them ahead of their first use (a guess
         costs processor time only: a library is still built when it is first asked for)."""
+        own = []                                    # libraries that parts name themselves (``kernel_modules`` of a class)
+        def walk(p):
+            for m in getattr(p, "kernel_modules", ()):
+                if m not in own:
+                    own.append(m)
+            for c in p.children():
+                walk(c)
+        for p in self.parts():
+            walk(p)
         if act_dtype != torch.bfloat16:
-            return ["generic"]
-        mods = ["generic", "gemv", "attention", "tc_gemm", "tc_stream"]
-        head_sizes = {layer.mixer.params.get("head_dim") for layer in self.spec.layers}
+            return ["generic"] + own
+        mods = ["generic", "gemv", "tc_gemm", "tc_stream"] + own
+        kinds = {layer.mixer.kind for layer in self.spec.layers}
+        if "attention" in kinds:
+            mods.append("attention")
+        head_sizes = {layer.mixer.params.get("head_dim") for layer in self.spec.layers if layer.mixer.kind == "attention"}
         if head_sizes & {64, 128}:                  # the tcgen05 prompt attention, the one-kernel decode path, the C++ launcher
             mods += ["flash_tc", "decode_layers", "host_step"]
         return mods
@@ -103,6 +116,9 @@ class Model:
         else:
             with phase("embedding_ms"):
                 h = self.embedding.forward(step)
+        h0 = None
+        if any(e.adds_embedding for e in self.spec.schedule):
+            h0 = h.clone()                                 # what the embedding left, for the runs that take it in again
         if one_kernel:
             done = self._fused.run(h, step, cache, greedy, note)
             if done is not None:
@@ -114,6 +130,8 @@ class Model:
             self._fused_prefill.run(h, step, cache)
         else:
             for e in self.spec.schedule:
+                if e.adds_embedding:
+                    K.add_inplace(h, h0)
                 self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))
         if step.n_want == 0:
             if greedy:
@@ -128,7 +146,6 @@ class Model:
             tokens = self.head.greedy(x, note) if hasattr(self.head, "greedy") else None
         if tokens is None:
             # a head without such a kernel, or operands it does not take (32-bit, odd sizes): the logits, then their argmax
-            from ..csrc import lib as K
             logits = self.head.forward(x)
             tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
             K.argmax_rows(logits, tokens)

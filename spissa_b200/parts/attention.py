@@ -60,6 +60,8 @@ class GQAAttention(Mixer):
         n.update(names or {})
         self.names = {k: prefix + v for k, v in n.items()}
         self.position = build_part("position", position) if position is not None else None
+        if getattr(self.position, "pairing", "half") != "half":
+            raise ValueError(f"{prefix}: this mixer's kernels rotate dim i with dim i + rotary_dim/2 only")
         self.qkv = self.o = None
 
     def children(self):

@@ -14,7 +14,7 @@ Interfaces (duck-typed; the base classes hold the shared plumbing only):
   so that the attention mixer can rotate while it writes the cache, or implements
   ``apply(qkv, step, num_heads, num_kv_heads, head_dim)`` which changes q and k in
   place.
-* ``Mixer.cache_request()`` -> ``KVCacheRequest`` | ``StateRequest`` | None, and
+* ``Mixer.cache_request()`` -> ``KVCacheRequest`` | ``StateRequest`` | ``CacheBundle`` | None, and
   ``Mixer.forward(x, step, cache, residual)``: reads the normed ``x`` [T, H], ADDS its
   result into ``residual`` (32-bit, [T, H]) in place. ``cache`` is the view of this
   run's cache (``cache.views.KVLayerView`` / ``StateLayerView``) or None.
@@ -40,10 +40,17 @@ class WeightSpec:
 
 @dataclass(frozen=True)
 class KVCacheRequest:
-    """Keys and values of every visible position; ``window`` None means all of them."""
+    """Keys and values of every visible position; ``window`` None means all of them.
+
+    ``head_dim`` is the size of a key row per kv head, ``v_head_dim`` that of a value row when it differs.
+    ``keep_first``: with a window, the first ``keep_first`` positions stay visible to every later query, so the pages
+    that hold them are never handed back while the sequence lives.
+    """
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -51,6 +58,18 @@ class StateRequest:
     """A fixed-size state per sequence, zeroed when a sequence starts."""
     shape: tuple
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CacheBundle:
+    """Several caches for one run of a layer, by name: ``parts`` is a tuple of (name, request) with requests of the
+    kinds above (a ``None`` request is left out). The run's view is then a ``BundleView`` whose ``[name]`` is the
+    view that the request alone would have got."""
+    parts: tuple
+
+    @staticmethod
+    def of(**named) -> "CacheBundle":
+        return CacheBundle(tuple((k, v) for k, v in named.items() if v is not None))
 
 
 @dataclass

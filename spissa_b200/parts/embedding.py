@@ -1,7 +1,7 @@
 """Token embedding and output head.
 
-Embedding: h[t,:] = E[id_t,:], no scale (crates/spissa-runtime/src/ops.rs:6-30); the
-rows enter the 32-bit residual stream. Head: logits = x · Wᵀ with W either its own
+Embedding: h[t,:] = E[id_t,:] (crates/spissa-runtime/src/ops.rs:6-30), times ``scale`` where a
+model has one (1, the default, for the reference's models); the rows enter the 32-bit residual stream. Head: logits = x · Wᵀ with W either its own
 tensor or the embedding table when the model ties them
 (crates/spissa-runtime/src/models/llama/api.rs:176-181, :336-346); logits are 32-bit.
 """
@@ -19,10 +19,12 @@ from .registry import register_part
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, prefix: str = "", weight_name: str = "weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, prefix: str = "", weight_name: str = "weight",
+                 scale: float = 1.0):
         super().__init__(prefix)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.weight_name = prefix + weight_name
+        self.scale = float(scale)                  # multiplies the rows on their way into the stream (not the table)
         self.weight = None
 
     def weight_specs(self):
@@ -34,7 +36,8 @@ class TokenEmbedding(Part):
 
     def fused_fields(self):
         """What a runner that gathers the rows itself needs: the table [vocab, hidden] (bfloat16)."""
-        if self.weight is None or self.weight.dtype != torch.bfloat16 or type(self) is not TokenEmbedding:
+        if self.weight is None or self.weight.dtype != torch.bfloat16 or type(self) is not TokenEmbedding \
+                or self.scale != 1.0:
             return None
         return dict(kind="token_embedding", weight=self.weight, vocab_size=self.vocab_size, hidden_size=self.hidden_size)
 
@@ -44,7 +47,7 @@ class TokenEmbedding(Part):
         and a fault code in the device's status word (ids that come from the host are checked there already)."""
         ids = step.tokens
         out = torch.empty(ids.shape[0], self.hidden_size, dtype=torch.float32, device=ids.device)
-        K.embed_gather(self.weight, ids, out, K.status_word(ids.device))
+        K.embed_gather(self.weight, ids, out, K.status_word(ids.device), self.scale)
         return out
 
 

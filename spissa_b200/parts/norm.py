@@ -1,7 +1,11 @@
-"""RMS norm: y = x / sqrt(mean(x²) + eps) · w, statistics in 32-bit.
+"""Norms of the residual stream.
 
-crates/spissa-runtime/src/ops.rs:159-179 (eps inside the root, the weight multiplies
+RMS norm: y = x / sqrt(mean(x²) + eps) · w, statistics in 32-bit
+(crates/spissa-runtime/src/ops.rs:159-179: eps inside the root, the weight multiplies
 directly, no ``1 + w``).
+
+Dynamic tanh: y = tanh(alpha · x) ⊙ w + b with a learned scalar alpha: a norm that takes
+no mean and no variance, so a token's row needs no reduction (not in the reference).
 """
 from __future__ import annotations
 
@@ -39,4 +43,42 @@ class RMSNorm(Norm):
         n = h.shape[0] if rows is None else rows.shape[0]
         out = torch.empty(n, self.size, dtype=self.rt.act_dtype, device=h.device)
         K.rmsnorm(h, self.weight, out, self.eps, rows)
+        return out
+
+
+@register_part("norm", "dyt")
+class DynamicTanh(Norm):
+    """``weight_name`` / ``bias_name`` / ``alpha_name`` are appended to the prefix (the weight's may be empty: some
+    checkpoints store it under the norm's own name)."""
+    graph_safe = True
+    kernel_modules = ("seqmix",)
+
+    def __init__(self, size: int, prefix: str = "", weight_name: str = "weight", bias_name: str = "bias",
+                 alpha_name: str = "alpha"):
+        super().__init__(prefix)
+        self.size = int(size)
+        self.names = dict(w=prefix + weight_name, b=prefix + bias_name, a=prefix + alpha_name)
+        self.weight = self.bias = self.alpha = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.names["w"], (self.size,), init="ones"), WeightSpec(self.names["b"], (self.size,)),
+                WeightSpec(self.names["a"], (), init="const:0.5")]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors[self.names["w"]].contiguous()
+        self.bias = tensors[self.names["b"]].contiguous()
+        self.alpha = tensors[self.names["a"]].reshape(1).contiguous()
+        if not (self.weight.dtype == self.bias.dtype == self.alpha.dtype):
+            raise ValueError(f"{self.prefix}: weight, bias and alpha must share a storage type")
+
+    def fused_fields(self):
+        if self.weight is None:
+            return None
+        return dict(kind="dyt", weight=self.weight, bias=self.bias, alpha=self.alpha, size=self.size)
+
+    def forward(self, h: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        n = h.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty(n, self.size, dtype=self.rt.act_dtype, device=h.device)
+        K.dyt_norm(h, self.weight, self.bias, self.alpha, out, rows)
         return out

@@ -1,4 +1,5 @@
-"""Rotary position encoding, rotate-half: dim i pairs with i + rotary_dim/2.
+"""Rotary position encoding. ``pairing`` "half" (the default): dim i pairs with i + rotary_dim/2;
+"interleaved": dim 2i pairs with dim 2i+1. Either way pair i turns by position · inv_freq_i.
 
 angle = position · inv_freq_i with inv_freq_i = 1 / θ^(2i/rotary_dim), all in 32-bit
 (crates/spissa-runtime/src/rotary.rs:454-465); the rotation itself happens in the
@@ -51,8 +52,12 @@ def rotary_inv_freq(theta: float, rotary_dim: int, scaling: dict | None) -> torc
 class RotaryEncoding(PositionEncoding):
     graph_safe = True
 
-    def __init__(self, theta: float, rotary_dim: int, scaling: dict | None = None, prefix: str = ""):
+    def __init__(self, theta: float, rotary_dim: int, scaling: dict | None = None, prefix: str = "",
+                 pairing: str = "half"):
         super().__init__(prefix)
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotary pairing is 'half' or 'interleaved', got {pairing!r}")
+        self.pairing = pairing                  # which dims form a pair; the mixer's kernel must know the layout
         self.theta = float(theta)
         self.rotary_dim = int(rotary_dim)
         self.scaling = dict(scaling) if scaling else None

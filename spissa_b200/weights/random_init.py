@@ -24,6 +24,8 @@ def random_tensors(specs: list, seed: int, std: float = 0.02, norm_std: float = 
     for s in sorted({s.name: s for s in specs}.values(), key=lambda s: s.name):
         if s.kind == "int":
             out[s.name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
+        elif s.init.startswith("const:"):              # a fixed value (a scalar or a table that must not be random)
+            out[s.name] = torch.full(s.shape, float(s.init[6:]), dtype=torch.float32, device=device).to(dtype)
         elif s.init == "ones":
             t = torch.ones(s.shape, dtype=torch.float32, device=device)
             if norm_std > 0:
