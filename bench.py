@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b] [--batch B]
                     [--context T] [--profile-phases]
+    python bench.py --design duzinex [--design-sizes 1k,2k,4k]      (the Duzinex decoder beside Llama at equal sizes)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 from prompts of
 about 2,048 tokens in a cache of 4,096 tokens per sequence, timed on the device with CUDA
@@ -164,6 +165,183 @@ def ragged_lengths(batch, seed):
 
 KERNEL_CASE_LAYERS = 0
 KERNEL_CASE_BATCH = 0          # sequences of --kernel-case decode_layers (0: eight)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# --design duzinex: the Duzinex decoder beside the Llama decoder at equal layer sizes (random weights)
+DESIGN_SIZES = {
+    # width, ff, (attention: heads, kv heads, map size, value size), (retention: heads, dim, vdim), Llama heads / kv / head
+    "1k": dict(width=1024, ff=4096, att=(8, 2, 64, 128), ret=(4, 128, 256), llama=(16, 4, 64)),
+    "2k": dict(width=2048, ff=8192, att=(16, 4, 64, 128), ret=(8, 128, 256), llama=(32, 8, 64)),
+    "4k": dict(width=4096, ff=14336, att=(32, 8, 64, 128), ret=(16, 128, 256), llama=(32, 8, 128)),
+}
+DESIGN_WINDOW = 1024
+DESIGN_VOCAB = 32000
+
+
+def duzinex_config(size: dict, window: int = DESIGN_WINDOW) -> dict:
+    W, ff = size["width"], size["ff"]
+    h, g, d, vd = size["att"]
+    rh, rd, rvd = size["ret"]
+    att = dict(type="attention", mixer=dict(heads=h, kv_heads=g, dim=d, vdim=vd, diff=0.5, scale=d ** -0.5, softcap=30.0,
+                                            mask=dict(size=window, keep_first=4), rot=dict(dims=d, base=10000.0)))
+    ret = dict(type="retention", mixer=dict(heads=rh, dim=rd, vdim=rvd,
+                                            decay=[1.0 - 2.0 ** (-5 - i % 4) for i in range(rh)]))
+    gru = dict(type="mingru", mixer=dict(width=W))
+    mlp = dict(kind="dense", ff=ff)
+    layers = [dict(l, mlp=mlp) for l in (ret, gru, att, gru, att, ret)]
+    # layers 1 … 4 run twice: ten layer runs (2 of retention, 4 of minGRU, 4 of attention)
+    return dict(architecture="Duzinex", vocab=DESIGN_VOCAB, width=W, embedding=dict(scale=W ** 0.5), norm=dict(eps=1e-6),
+                layers=layers, loop=dict(start=1, stop=5, times=2))
+
+
+def llama_config_like(size: dict, layers: int) -> dict:
+    nh, nkv, hd = size["llama"]
+    return dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=layers, hidden_size=size["width"],
+                num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, intermediate_size=size["ff"],
+                vocab_size=DESIGN_VOCAB, rope_theta=10000.0, rope_scaling=None, tie_word_embeddings=True,
+                rms_norm_eps=1e-6, max_position_embeddings=131072)
+
+
+def design_compare(args) -> int:
+    """Prefill (one 2,048-token prompt) and decode (batch 8 behind such prompts) of the Duzinex decoder and of the
+    Llama decoder with the same width, feed-forward size and number of layer runs; per-phase device times of both
+    (CUDA events around kernel groups, steps run part by part), and for the new design's own kernels the bytes or
+    FLOPs they have to move against the measured peaks. Prints ONE JSON line."""
+    import torch
+    from spissa_b200 import Engine
+    from spissa_b200.config import config_from_dict
+    from spissa_b200.csrc import lib
+    peaks = load_peaks()
+    torch.cuda.set_device(0)
+    T, B = PREFILL_TOKENS, 8
+    out = {"design": "duzinex", "beside": "llama", "dtype": args.dtype, "prefill_tokens": T, "decode_batch": B,
+           "window": DESIGN_WINDOW, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops", "source")}, "sizes": {}}
+    names = [n for n in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES) if n in DESIGN_SIZES]
+    for name in names:
+        size = DESIGN_SIZES[name]
+        dz = duzinex_config(size)
+        runs = len(config_from_dict(dz).to_spec().schedule)
+        row = {}
+        for label, cfg_dict in (("duzinex", dz), ("llama", llama_config_like(size, runs))):
+            cfg = config_from_dict(cfg_dict)
+            engine = Engine.from_config(cfg, seed=0, dtype=args.dtype, max_tokens=B * (T + 128), max_seqs=B, device="cuda:0")
+            rng = random.Random(7)
+            V = DESIGN_VOCAB
+            prompt = [rng.randrange(V) for _ in range(T)]
+
+            def prefill_once():
+                s = engine.acquire()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                engine.step([(s, prompt, [T - 1])], check=False)
+                e1.record()
+                torch.cuda.synchronize()
+                engine.check()
+                engine.release(s)
+                return e0.elapsed_time(e1)
+
+            for _ in range(3):
+                prefill_once()
+            pre_ms = sorted(prefill_once() for _ in range(5))[2]
+            slots = [engine.acquire() for _ in range(B)]
+            for s in slots:
+                engine.step([(s, [rng.randrange(V) for _ in range(T)], [])], check=False)
+            engine.check()
+            one = lambda: engine.step([(s, [11], [0]) for s in slots], check=False)
+            for _ in range(max(3, args.warmup)):
+                one()
+            torch.cuda.synchronize()
+            steps = args.steps or 32
+            l0 = lib.launches
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                one()
+            e1.record()
+            torch.cuda.synchronize()
+            engine.check()
+            dec_ms = e0.elapsed_time(e1) / steps
+            launches = (lib.launches - l0) // steps
+            # per-phase times, steps run part by part
+            engine.profile_phases = True
+            engine.phase_totals.clear()
+            for sl in slots:
+                engine.release(sl)
+            s = engine.acquire()
+            engine.step([(s, prompt, [T - 1])])
+            pre_phases = dict(engine.phase_totals["prefill"]["ms"])
+            engine.release(s)
+            slots = [engine.acquire() for _ in range(B)]
+            engine.step([(sl, prompt[:T - 8], []) for sl in slots])
+            engine.phase_totals.pop("decode", None)
+            for i in range(4):
+                engine.step([(sl, [7 + i], [0]) for sl in slots])
+            dec_phases = {k: v / 4 for k, v in engine.phase_totals["decode"]["ms"].items()}
+            for sl in slots:
+                engine.release(sl)
+            engine.profile_phases = False
+            weight_bytes = sum(t.numel() * t.element_size() for t in
+                               {id(p.weight): p.weight for p in _linears(engine.model)}.values())
+            row[label] = dict(layer_runs=runs, prefill_ms=round(pre_ms, 3), prefill_tok_s=round(T / pre_ms * 1e3, 1),
+                              decode_ms_per_step=round(dec_ms, 4), decode_tok_s=round(B / dec_ms * 1e3, 1),
+                              decode_launches_per_step=launches, weight_gb=round(weight_bytes / 1e9, 3),
+                              decode_weight_stream_frac=round(weight_bytes / (dec_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                              prefill_phases_ms={k: round(v, 4) for k, v in sorted(pre_phases.items())},
+                              decode_phases_ms={k: round(v, 4) for k, v in sorted(dec_phases.items())})
+            del engine
+            torch.cuda.empty_cache()
+        row["rooflines"] = design_rooflines(size, row, T, B, peaks, 4 if args.dtype == "float32" else 2)
+        out["sizes"][name] = row
+    print(json.dumps(out))
+    return 0
+
+
+def _linears(model):
+    found = []
+
+    def walk(p):
+        for v in vars(p).values():
+            if hasattr(v, "weight") and hasattr(v, "out_features"):
+                found.append(v)
+            elif hasattr(v, "plain") and hasattr(v.plain, "out_features"):
+                found.append(v.plain)
+        for c in p.children():
+            walk(c)
+    for p in model.parts():
+        walk(p)
+    return found
+
+
+def design_rooflines(size, row, T, B, peaks, eb) -> dict:
+    """What each kernel group of a prompt step has to do at least, as a fraction of the measured peaks, for the new
+    design's own kernels and the Llama kernels that are most like them. Per-phase times are sums over the layer runs."""
+    h, g, d, vd = size["att"]
+    rh, rd, rvd = size["ret"]
+    W, ff = size["width"], size["ff"]
+    nh, nkv, hd = size["llama"]
+    dz, ll = row["duzinex"]["prefill_phases_ms"], row["llama"]["prefill_phases_ms"]
+    tf, bw = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    win = min(T, DESIGN_WINDOW)
+    pairs = T * win - win * (win - 1) / 2                       # (query, visible key) pairs of one window, first tokens aside
+    frac = lambda work, peak, ms: round(work / (ms * 1e-3) / peak, 4) if ms else None
+    out = {}
+    # four attention runs: two maps of d MACs per pair for the scores, two maps of vd MACs for the values
+    att_flops = 4 * h * pairs * (2 * 2 * d + 2 * 2 * vd)
+    out["diff_attention (tensor)"] = dict(ms=dz.get("attention_ms"), frac=frac(att_flops, tf, dz.get("attention_ms")))
+    ll_att = ll.get("attention_ms")
+    ll_runs = row["llama"]["layer_runs"]
+    out["llama attention (tensor)"] = dict(ms=ll_att, frac=frac(ll_runs * 4.0 * (T * (T + 1) / 2) * hd * nh, tf, ll_att))
+    # retention: two runs; chunked form: per token and head d·vd MACs for the state, the same for the read, plus the
+    # chunk's own pairs; counted as the recurrence's 2·2·d·vd FLOPs per token and head (the least any form does)
+    out["retention (tensor)"] = dict(ms=dz.get("retention_ms"), frac=frac(2 * T * rh * 4.0 * rd * rvd, tf, dz.get("retention_ms")))
+    out["retention (hbm)"] = dict(ms=dz.get("retention_ms"),
+                                  frac=frac(2 * T * (2 * rh * rd + 2 * rh * rvd) * 4.0 + 2 * T * rh * rvd * eb, bw, dz.get("retention_ms")))
+    out["mingru (hbm)"] = dict(ms=dz.get("mingru_ms"), frac=frac(4 * T * W * (3 * 4.0 + eb), bw, dz.get("mingru_ms")))
+    out["polynorm (hbm)"] = dict(ms=dz.get("activation_ms"), frac=frac(10 * T * ff * (4.0 + eb), bw, dz.get("activation_ms")))
+    out["norm+shift (hbm)"] = dict(ms=dz.get("mixer_norm+shift_ms"), frac=frac(10 * T * W * (4.0 + eb), bw, dz.get("mixer_norm+shift_ms")))
+    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    return out
 
 
 def kernel_case(name: str, reps: int) -> int:
@@ -464,6 +642,9 @@ def main() -> int:
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
                          "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
+    ap.add_argument("--design", default=None, choices=["duzinex"],
+                    help="measure this design beside the Llama decoder at equal layer sizes instead of the headline workload")
+    ap.add_argument("--design-sizes", default="", dest="design_sizes", help="which of 1k,2k,4k (default: all)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()
@@ -472,6 +653,9 @@ def main() -> int:
         KERNEL_CASE_LAYERS = args.case_layers
         KERNEL_CASE_BATCH = args.batch or 0
         return kernel_case(args.kernel_case, args.reps)
+
+    if args.design:
+        return design_compare(args)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -54,6 +54,7 @@ MODULES = {
     "tc_stream": "tc_stream.cu",
     "host_step": "host_step.cu",
     "seqmix": "seqmix_kernels.cu",
+    "diff_flash": "diff_flash.cu",
 }
 
 

@@ -42,6 +42,8 @@ def load(module: str) -> ctypes.CDLL:
         except OSError as e:
             raise KernelError(f"cannot load kernel library {path}: {e}") from None
         getattr(lib, f"sp_{module}_last_error").restype = ctypes.c_char_p
+        if module == "seqmix":
+            lib.sp_retention_chunked_scratch_floats.restype = c_longlong
         _LIBS[module] = lib
         _LOADED_PATHS[module] = str(path)
         checked = getattr(lib, f"sp_{module}_range_checked", None)
@@ -881,10 +883,34 @@ def retention(proj, state, decay, out, step, H, d, vd, eps):
     if proj.dtype != torch.float32 or state.dtype != torch.float32 or decay.dtype != torch.float32:
         raise KernelError("retention runs on 32-bit projections, state and decays")
     _need_contig(proj, state, decay, out)
+    if not step.all_single and step.max_new >= CHUNKED_FROM and retention_chunked_supported(d, vd):
+        # a prompt: chunks of 64 tokens in parallel (FFMA tiles), their start states by a short scan
+        global launches
+        launches += 3
+        n_chunks, T = _chunks(step), proj.shape[0]
+        need = lib.sp_retention_chunked_scratch_floats(n_chunks, T, H, d, vd)
+        scratch = torch.empty(need, dtype=torch.float32, device=proj.device)
+        _check("seqmix", lib.sp_retention_chunked(
+            c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(decay)),
+            c_void_p(_ptr(scratch)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)),
+            c_void_p(_ptr(step.seq_slot)), step.n_seqs, T, n_chunks, H, d, vd, c_float(eps), c_void_p(_stream())))
+        return
     _check("seqmix", lib.sp_retention(
         c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(decay)),
         c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), step.n_seqs,
         H, d, vd, c_float(eps), c_void_p(_stream())))
+
+
+CHUNK_TOKENS = 64            # tokens per chunk of the chunked recurrences
+CHUNKED_FROM = 32            # a step's longest portion from which the recurrences run in chunks
+
+
+def _chunks(step) -> int:
+    return query_tiles(step.host["new_counts"], CHUNK_TOKENS)
+
+
+def retention_chunked_supported(d: int, vd: int) -> bool:
+    return bool(load("seqmix").sp_retention_chunked_supported(d, vd))
 
 
 def mingru(proj, z_bias, x_bias, state, out, step, W):
@@ -893,6 +919,17 @@ def mingru(proj, z_bias, x_bias, state, out, step, W):
     if proj.dtype != torch.float32 or state.dtype != torch.float32:
         raise KernelError("mingru runs on 32-bit projections and state")
     _need_contig(proj, z_bias, x_bias, state, out)
+    if not step.all_single and step.max_new >= CHUNKED_FROM:
+        # a prompt: chunks of 64 tokens in parallel, their start states by a short scan
+        global launches
+        launches += 2
+        n_chunks = _chunks(step)
+        scratch = torch.empty(n_chunks * W * 2, dtype=torch.float32, device=proj.device)
+        _check("seqmix", lib.sp_mingru_chunked(
+            c_void_p(_ptr(proj)), c_void_p(_ptr(z_bias)), c_void_p(_ptr(x_bias)), _w_dt(z_bias, x_bias),
+            c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(scratch)), c_void_p(_ptr(out)), dt_code(out),
+            c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), step.n_seqs, n_chunks, W, c_void_p(_stream())))
+        return
     _check("seqmix", lib.sp_mingru(
         c_void_p(_ptr(proj)), c_void_p(_ptr(z_bias)), c_void_p(_ptr(x_bias)), _w_dt(z_bias, x_bias), c_void_p(_ptr(state)),
         state.shape[0], c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)),
@@ -918,3 +955,28 @@ def add_bias(x, bias):
     _need_contig(x, bias)
     _check("seqmix", lib.sp_add_bias(c_void_p(_ptr(x)), c_void_p(_ptr(bias)), dt_code(bias), x.shape[0], x.shape[1],
                                      c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ diff_flash: differential attention of prompt steps
+def diff_flash_supported(d: int, vd: int, H: int, G: int, page_size: int) -> bool:
+    return bool(load("diff_flash").sp_diff_flash_supported(d, vd, H, G, page_size))
+
+
+def diff_flash_query_tile() -> int:
+    return int(load("diff_flash").sp_diff_flash_query_tile())
+
+
+def diff_flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, H, G, d, vd, window, keep_first,
+                       scale, softcap, lam, eps, out_scale):
+    """``diff_attention`` for the tokens of prompts (bfloat16 q and cache), 64 queries per CTA on the tensor cores."""
+    lib = load("diff_flash")
+    _need_contig(q, out)
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("diff_flash_prefill takes bfloat16 queries, cache and output")
+    pt = meta.page_table
+    _declare_bounds("diff_flash", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
+    _check("diff_flash", lib.sp_diff_flash_prefill(
+        c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), c_void_p(_ptr(seq_start)),
+        c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
+        n_seqs, n_q_tiles, H, G, d, vd, int(window or 0), int(keep_first or 0), c_float(scale), c_float(softcap or 0.0),
+        c_float(lam), c_float(eps), c_float(out_scale), c_void_p(_stream())))

@@ -482,6 +482,264 @@ SP_API int sp_retention(const float* proj, int ld, float* state, int n_slots, co
     return 0;
 }
 
+// ============================================================== retention of a prompt step, in chunks of 64 tokens
+// The recurrence unrolled over a chunk that starts at token t0 with the state S (all sums in 32-bit FFMA):
+//   o_{t0+i} = γ^{i+1} · Sᵀ q_i  +  Σ_{j ≤ i} γ^{i−j} (q_i · k_j) v_j            (k already divided by √d)
+//   S'       = γ^{n} · S  +  Σ_j γ^{n−1−j} k_j v_jᵀ                               (n tokens in the chunk)
+// Four launches: (A) every chunk's own Σ_j γ^{n−1−j} k_j v_jᵀ, in parallel; (B) per (sequence, head) the chunks'
+// start states one after the other (element by element, cheap), the last one becomes the slot's state; (C) every
+// chunk's outputs from its start state, in parallel; (D) unit rms per head, the gate, the store. A chunk's arithmetic
+// depends on where the chunk starts in its step only, so the same tokens cut into other steps differ by rounding.
+// All products are tiles of out[m][n] = Σ_k a[k][m]·b[k][n] with a and b in shared memory, k-major, 16 x 16 threads
+// owning 4·MA x 4·NB outputs each.
+#define RC_CHUNK 64
+
+template <int MA, int NB>
+__device__ __forceinline__ void rc_mm(const float* __restrict__ a, int lda, const float* __restrict__ b, int ldb, int K,
+                                      float (&acc)[4 * MA][4 * NB], int ty, int tx) {
+    for (int k = 0; k < K; ++k) {
+        float4 av[MA], bv[NB];
+#pragma unroll
+        for (int i = 0; i < MA; ++i) av[i] = *(const float4*)(a + (size_t)k * lda + 4 * ty + 64 * i);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) bv[j] = *(const float4*)(b + (size_t)k * ldb + 4 * tx + 64 * j);
+#pragma unroll
+        for (int i = 0; i < MA; ++i) {
+            const float am[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const float bn[4] = {bv[j].x, bv[j].y, bv[j].z, bv[j].w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) acc[4 * i + u][4 * j + v] = fmaf(am[u], bn[v], acc[4 * i + u][4 * j + v]);
+            }
+        }
+    }
+}
+
+struct RcArgs {
+    const float* proj; int ld;         // rows [q | k | v | g]
+    float* state;                      // [slots][H][d][vd]
+    const float* decay;                // [H]
+    float* chunk_state;                // [chunks][H][d][vd]: (A) the chunk's own sum, (B) turns it into its start state
+    float* o_raw;                      // [T][H·vd]
+    void* out; int out_dt;
+    const int* seq_start; const int* seq_slot;
+    int B, H, d, vd, n_slots, n_chunks;
+    float eps;
+};
+
+// which sequence, which chunk of it, its first token and its length
+__device__ __forceinline__ bool rc_chunk_of(const RcArgs& a, int x, int& s, int& t0, int& n) {
+    for (s = 0; s < a.B; ++s) {
+        const int first = a.seq_start[s], cnt = a.seq_start[s + 1] - first;
+        const int nc = (cnt + RC_CHUNK - 1) / RC_CHUNK;
+        if (x < nc) {
+            t0 = first + x * RC_CHUNK;
+            n = min(RC_CHUNK, cnt - x * RC_CHUNK);
+            return true;
+        }
+        x -= nc;
+    }
+    return false;
+}
+
+// (A) grid (chunks, H, column blocks of 64·NB); MA = ceil(d / 64)
+template <int MA, int NB>
+__global__ void __launch_bounds__(256) retention_chunk_sum_kernel(RcArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int DP = 64 * MA, NP = 64 * NB;
+    float* kd = sm;                    // [64][DP]   γ^{n−1−j} k_j / √d
+    float* vv = kd + RC_CHUNK * DP;    // [64][NP]
+    int s, t0, n;
+    if (!rc_chunk_of(a, blockIdx.x, s, t0, n)) return;
+    const int h = blockIdx.y, c0 = blockIdx.z * NP;
+    const int d = a.d, vd = a.vd, Hd = a.H * d;
+    const float gamma = a.decay[h], kscale = 1.0f / sqrtf((float)d);
+    for (int e = threadIdx.x; e < RC_CHUNK * DP; e += 256) {
+        const int j = e / DP, i = e - j * DP;
+        kd[e] = (j < n && i < d) ? a.proj[(size_t)(t0 + j) * a.ld + Hd + h * d + i] * kscale * powf(gamma, (float)(n - 1 - j)) : 0.0f;
+    }
+    for (int e = threadIdx.x; e < RC_CHUNK * NP; e += 256) {
+        const int j = e / NP, c = e - j * NP;
+        vv[e] = (j < n && c0 + c < vd) ? a.proj[(size_t)(t0 + j) * a.ld + 2 * Hd + h * vd + c0 + c] : 0.0f;
+    }
+    __syncthreads();
+    float acc[4 * MA][4 * NB];
+#pragma unroll
+    for (int i = 0; i < 4 * MA; ++i)
+#pragma unroll
+        for (int j = 0; j < 4 * NB; ++j) acc[i][j] = 0.0f;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    rc_mm<MA, NB>(kd, DP, vv, NP, n, acc, ty, tx);
+    float* dst = a.chunk_state + ((size_t)blockIdx.x * a.H + h) * d * vd;
+#pragma unroll
+    for (int i = 0; i < 4 * MA; ++i) {
+        const int r = 4 * ty + 64 * (i >> 2) + (i & 3);
+#pragma unroll
+        for (int j = 0; j < 4 * NB; ++j) {
+            const int c = c0 + 4 * tx + 64 * (j >> 2) + (j & 3);
+            if (r < d && c < vd) dst[(size_t)r * vd + c] = acc[i][j];
+        }
+    }
+}
+
+// (B) grid (B, H, pieces of d·vd)
+__global__ void retention_chunk_scan_kernel(RcArgs a) {
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= a.d * a.vd) return;
+    int c = 0;                                              // the sequence's first chunk among all chunks of the step
+    for (int b = 0; b < s; ++b) c += (a.seq_start[b + 1] - a.seq_start[b] + RC_CHUNK - 1) / RC_CHUNK;
+    const int cnt = a.seq_start[s + 1] - a.seq_start[s];
+    const float gamma = a.decay[h];
+    float* gS = a.state + ((size_t)slot * a.H + h) * a.d * a.vd + e;
+    float S = *gS;
+    for (int x = 0; x * RC_CHUNK < cnt; ++x, ++c) {
+        const int n = min(RC_CHUNK, cnt - x * RC_CHUNK);
+        float* p = a.chunk_state + ((size_t)c * a.H + h) * a.d * a.vd + e;
+        const float own = *p;
+        *p = S;
+        S = fmaf(powf(gamma, (float)n), S, own);
+    }
+    *gS = S;
+}
+
+// (C) grid (chunks, H, column blocks of 64·NB); MA = ceil(d / 64) sizes the shared arrays only
+template <int NB>
+__global__ void __launch_bounds__(256) retention_chunk_out_kernel(RcArgs a, int DP) {
+    extern __shared__ __align__(16) float sm[];
+    const int NP = 64 * NB;
+    float* qT = sm;                         // [DP][64]
+    float* kT = qT + (size_t)DP * 64;       // [DP][64]   k / √d
+    float* S = kT + (size_t)DP * 64;        // [DP][NP]
+    float* vv = S + (size_t)DP * NP;        // [64][NP]
+    float* pT = vv + 64 * NP;               // [64 keys][64 queries]
+    __shared__ float pw[RC_CHUNK + 1];
+    int s, t0, n;
+    if (!rc_chunk_of(a, blockIdx.x, s, t0, n)) return;
+    const int h = blockIdx.y, c0 = blockIdx.z * NP;
+    const int d = a.d, vd = a.vd, Hd = a.H * d;
+    const float gamma = a.decay[h], kscale = 1.0f / sqrtf((float)d);
+    if (threadIdx.x <= RC_CHUNK) pw[threadIdx.x] = powf(gamma, (float)threadIdx.x);
+    for (int e = threadIdx.x; e < RC_CHUNK * DP; e += 256) {
+        const int j = e / DP, i = e - j * DP;               // token j, dim i: read along the dims, store transposed
+        const bool ok = j < n && i < d;
+        const float* row = a.proj + (size_t)(t0 + j) * a.ld;
+        qT[i * 64 + j] = ok ? row[h * d + i] : 0.0f;
+        kT[i * 64 + j] = ok ? row[Hd + h * d + i] * kscale : 0.0f;
+    }
+    const float* gS = a.chunk_state + ((size_t)blockIdx.x * a.H + h) * d * vd;
+    for (int e = threadIdx.x; e < DP * NP; e += 256) {
+        const int i = e / NP, c = e - i * NP;
+        S[e] = (i < d && c0 + c < vd) ? gS[(size_t)i * vd + c0 + c] : 0.0f;
+    }
+    for (int e = threadIdx.x; e < RC_CHUNK * NP; e += 256) {
+        const int j = e / NP, c = e - j * NP;
+        vv[e] = (j < n && c0 + c < vd) ? a.proj[(size_t)(t0 + j) * a.ld + 2 * Hd + h * vd + c0 + c] : 0.0f;
+    }
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    {
+        // P[i][j] = γ^{i−j} q_i · k_j for j ≤ i, stored as pT[j][i]
+        float p[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) p[u][v] = 0.0f;
+        rc_mm<1, 1>(qT, 64, kT, 64, d, p, ty, tx);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int i = 4 * ty + u, j = 4 * tx + v;
+                pT[j * 64 + i] = (j <= i && i < n) ? p[u][v] * pw[i - j] : 0.0f;
+            }
+    }
+    __syncthreads();
+    float inter[4][4 * NB], intra[4][4 * NB];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < 4 * NB; ++v) inter[u][v] = intra[u][v] = 0.0f;
+    rc_mm<1, NB>(qT, 64, S, NP, d, inter, ty, tx);
+    rc_mm<1, NB>(pT, 64, vv, NP, n, intra, ty, tx);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = 4 * ty + u;
+        if (i >= n) continue;
+        const float gi = pw[i + 1];
+#pragma unroll
+        for (int v = 0; v < 4 * NB; ++v) {
+            const int c = c0 + 4 * tx + 64 * (v >> 2) + (v & 3);
+            if (c < vd) a.o_raw[(size_t)(t0 + i) * a.H * vd + h * vd + c] = fmaf(gi, inter[u][v], intra[u][v]);
+        }
+    }
+}
+
+// (D) grid (T, H): unit rms over the head's values, the gate, the store
+__global__ void retention_finish_kernel(RcArgs a, int T) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int vd = a.vd, Hv = a.H * vd;
+    const float* o = a.o_raw + (size_t)t * Hv + h * vd;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < vd; c += blockDim.x) ss = fmaf(o[c], o[c], ss);
+    ss = sp_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)vd + a.eps);
+    const float* g = a.proj + (size_t)t * a.ld + 2 * a.H * a.d + Hv + h * vd;
+    for (int c = threadIdx.x; c < vd; c += blockDim.x)
+        sp_st_dt(a.out, a.out_dt, (size_t)t * Hv + h * vd + c, o[c] * inv * sm_silu(g[c]));
+}
+
+SP_API int sp_retention_chunked_supported(int d, int vd) { return d > 0 && d <= 128 && vd > 0; }
+
+SP_API long long sp_retention_chunked_scratch_floats(int n_chunks, int T, int H, int d, int vd) {
+    return (long long)n_chunks * H * d * vd + (long long)T * H * vd;
+}
+
+SP_API int sp_retention_chunked(const float* proj, int ld, float* state, int n_slots, const float* decay, float* scratch,
+                                void* out, int out_dt, const int* seq_start, const int* seq_slot, int B, int T, int n_chunks,
+                                int H, int d, int vd, float eps, cudaStream_t stream) {
+    if (B <= 0 || T <= 0 || n_chunks <= 0) return 0;
+    if (!sp_retention_chunked_supported(d, vd)) SP_FAIL("retention (chunks): key size %d is beyond this kernel's limit 128", d);
+    RcArgs a{proj, ld, state, decay, scratch, scratch + (size_t)n_chunks * H * d * vd, out, out_dt, seq_start, seq_slot,
+             B, H, d, vd, n_slots, n_chunks, eps};
+    const int MA = d <= 64 ? 1 : 2, NB = vd <= 64 ? 1 : 2;
+    const int DP = 64 * MA, NP = 64 * NB;
+    const dim3 grid(n_chunks, H, (vd + NP - 1) / NP);
+    const size_t smem_a = (size_t)(RC_CHUNK * DP + RC_CHUNK * NP) * sizeof(float);
+    const size_t smem_c = ((size_t)2 * DP * 64 + (size_t)DP * NP + 64 * NP + 64 * 64) * sizeof(float);
+    static SpPerDevice ready;
+    if (!ready.done()) {
+        const int big = 200 * 1024;
+        if (cudaFuncSetAttribute(retention_chunk_sum_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big) != cudaSuccess ||
+            cudaFuncSetAttribute(retention_chunk_sum_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big) != cudaSuccess ||
+            cudaFuncSetAttribute(retention_chunk_sum_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big) != cudaSuccess ||
+            cudaFuncSetAttribute(retention_chunk_sum_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big) != cudaSuccess ||
+            cudaFuncSetAttribute(retention_chunk_out_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big) != cudaSuccess ||
+            cudaFuncSetAttribute(retention_chunk_out_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big) != cudaSuccess)
+            SP_FAIL("retention (chunks): cannot raise the shared memory limit");
+        ready.mark();
+    }
+    if (MA == 1 && NB == 1) retention_chunk_sum_kernel<1, 1><<<grid, 256, smem_a, stream>>>(a);
+    else if (MA == 1) retention_chunk_sum_kernel<1, 2><<<grid, 256, smem_a, stream>>>(a);
+    else if (NB == 1) retention_chunk_sum_kernel<2, 1><<<grid, 256, smem_a, stream>>>(a);
+    else retention_chunk_sum_kernel<2, 2><<<grid, 256, smem_a, stream>>>(a);
+    SP_CHECK_LAUNCH("retention_chunk_sum");
+    retention_chunk_scan_kernel<<<dim3(B, H, (d * vd + 255) / 256), 256, 0, stream>>>(a);
+    SP_CHECK_LAUNCH("retention_chunk_scan");
+    if (NB == 1) retention_chunk_out_kernel<1><<<grid, 256, smem_c, stream>>>(a, DP);
+    else retention_chunk_out_kernel<2><<<grid, 256, smem_c, stream>>>(a, DP);
+    SP_CHECK_LAUNCH("retention_chunk_out");
+    retention_finish_kernel<<<dim3(T, H), 128, 0, stream>>>(a, T);
+    SP_CHECK_LAUNCH("retention_finish");
+    return 0;
+}
+
 // ============================================================== minGRU, token by token
 // proj row (32-bit) = [z: W | x: W | g: W] without the biases. One thread per (sequence, channel).
 __global__ void mingru_scan_kernel(const float* __restrict__ proj, const void* __restrict__ zb, const void* __restrict__ xb,
@@ -512,6 +770,85 @@ SP_API int sp_mingru(const float* proj, const void* zb, const void* xb, int b_dt
     mingru_scan_kernel<<<dim3((W + threads - 1) / threads, B), threads, 0, stream>>>(proj, zb, xb, b_dt, state, n_slots, out,
                                                                                     out_dt, seq_start, seq_slot, B, W);
     SP_CHECK_LAUNCH("mingru");
+    return 0;
+}
+
+// ============================================================== minGRU of a prompt step, in chunks of 64 tokens
+// S_t = a_t S_{t-1} + b_t with a_t = 1 − z_t, b_t = z_t c_t composes: over a chunk S_end = A·S_start + Bsum with
+// A = Π a_t and Bsum the chunk run from zero. (1) every (chunk, channel) finds (A, Bsum); (2) per (sequence, channel)
+// the chunks' start states one after the other; (3) every (chunk, channel) runs again from its start state and writes.
+#define MG_CHUNK 64
+
+__device__ __forceinline__ bool mg_chunk_of(const int* seq_start, int B, int x, int& s, int& t0, int& n) {
+    for (s = 0; s < B; ++s) {
+        const int first = seq_start[s], cnt = seq_start[s + 1] - first;
+        const int nc = (cnt + MG_CHUNK - 1) / MG_CHUNK;
+        if (x < nc) {
+            t0 = first + x * MG_CHUNK;
+            n = min(MG_CHUNK, cnt - x * MG_CHUNK);
+            return true;
+        }
+        x -= nc;
+    }
+    return false;
+}
+
+// PASS 1: scratch[chunk][c] = (A, Bsum).  PASS 3: reads scratch[chunk][c].x as the start state and writes the outputs.
+template <int PASS>
+__global__ void mingru_chunk_kernel(const float* __restrict__ proj, const void* __restrict__ zb, const void* __restrict__ xb,
+                                    int b_dt, float2* __restrict__ scratch, void* __restrict__ out, int out_dt,
+                                    const int* __restrict__ seq_start, int B, int W) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    int s, t0, n;
+    if (c >= W || !mg_chunk_of(seq_start, B, blockIdx.y, s, t0, n)) return;
+    const float bz = sp_ld_dt(zb, b_dt, c), bx = sp_ld_dt(xb, b_dt, c);
+    float2* cell = scratch + (size_t)blockIdx.y * W + c;
+    float S = PASS == 1 ? 0.0f : cell->x, A = 1.0f;
+    for (int t = t0; t < t0 + n; ++t) {
+        const float* row = proj + (size_t)t * 3 * W;
+        const float z = sm_sigmoid(row[c] + bz);
+        const float u = row[W + c] + bx;
+        const float cand = u >= 0.0f ? u + 0.5f : sm_sigmoid(u);
+        S = (1.0f - z) * S + z * cand;
+        if (PASS == 1) A *= 1.0f - z;
+        else sp_st_dt(out, out_dt, (size_t)t * W + c, S * sm_silu(row[2 * W + c]));
+    }
+    if (PASS == 1) *cell = make_float2(A, S);
+}
+
+__global__ void mingru_chunk_scan_kernel(float2* __restrict__ scratch, float* __restrict__ state, int n_slots,
+                                         const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int B, int W) {
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= B || c >= W) return;
+    const int slot = seq_slot[s];
+    if (slot < 0 || slot >= n_slots) return;
+    int chunk = 0;
+    for (int b = 0; b < s; ++b) chunk += (seq_start[b + 1] - seq_start[b] + MG_CHUNK - 1) / MG_CHUNK;
+    const int cnt = seq_start[s + 1] - seq_start[s];
+    float S = state[(size_t)slot * W + c];
+    for (int x = 0; x * MG_CHUNK < cnt; ++x, ++chunk) {
+        float2* cell = scratch + (size_t)chunk * W + c;
+        const float2 ab = *cell;
+        cell->x = S;
+        S = fmaf(ab.x, S, ab.y);
+    }
+    state[(size_t)slot * W + c] = S;
+}
+
+SP_API int sp_mingru_chunked(const float* proj, const void* zb, const void* xb, int b_dt, float* state, int n_slots,
+                             float* scratch, void* out, int out_dt, const int* seq_start, const int* seq_slot, int B,
+                             int n_chunks, int W, cudaStream_t stream) {
+    if (B <= 0 || n_chunks <= 0) return 0;
+    const int threads = 128;
+    const dim3 grid((W + threads - 1) / threads, n_chunks);
+    mingru_chunk_kernel<1><<<grid, threads, 0, stream>>>(proj, zb, xb, b_dt, (float2*)scratch, out, out_dt, seq_start, B, W);
+    SP_CHECK_LAUNCH("mingru_chunk_1");
+    mingru_chunk_scan_kernel<<<dim3((W + threads - 1) / threads, B), threads, 0, stream>>>((float2*)scratch, state, n_slots,
+                                                                                         seq_start, seq_slot, B, W);
+    SP_CHECK_LAUNCH("mingru_chunk_scan");
+    mingru_chunk_kernel<3><<<grid, threads, 0, stream>>>(proj, zb, xb, b_dt, (float2*)scratch, out, out_dt, seq_start, B, W);
+    SP_CHECK_LAUNCH("mingru_chunk_3");
     return 0;
 }
 

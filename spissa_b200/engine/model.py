@@ -45,7 +45,10 @@ class Model:
         costs processor time only: a library is still built when it is first asked for)."""
         own = []                                    # libraries that parts name themselves (``kernel_modules`` of a class)
         def walk(p):
-            for m in getattr(p, "kernel_modules", ()):
+            names = tuple(getattr(p, "kernel_modules", ()))
+            if act_dtype == torch.bfloat16:
+                names += tuple(getattr(p, "kernel_modules_bf16", ()))
+            for m in names:
                 if m not in own:
                     own.append(m)
             for c in p.children():

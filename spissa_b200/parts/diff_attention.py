@@ -31,6 +31,7 @@ from ..phases import phase
 class DiffAttention(Mixer):
     graph_safe = True
     kernel_modules = ("seqmix",)
+    kernel_modules_bf16 = ("diff_flash",)          # the tensor-core kernel of prompt steps
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, diff: float,
                  scale: float, eps: float, softcap=None, window=None, keep_first: int = 0, position=None,
@@ -94,8 +95,14 @@ class DiffAttention(Mixer):
             K.diff_qkv_store(qkv, self.qkv_bias, q, cache.k_pool, cache.v_pool, cache, inv_freq, 2 * nh, 2 * g, g, d, vd, rd)
         with phase("attention_ms"):
             ctx = torch.empty(T, nh * vd, dtype=self.rt.act_dtype, device=x.device)
-            K.diff_attention(q, cache.k_pool, cache.v_pool, ctx, cache, nh, g, d, vd, self.window, self.keep_first,
-                             self.scale, self.softcap, self.lam, self.eps, 1.0 - self.diff)
+            args = (nh, g, d, vd, self.window, self.keep_first, self.scale, self.softcap, self.lam, self.eps, 1.0 - self.diff)
+            if (not step.all_single and q.dtype == torch.bfloat16 and cache.k_pool.dtype == torch.bfloat16
+                    and K.diff_flash_supported(d, vd, nh, g, cache.page_size)):
+                # a prompt step: 64 queries per CTA on the tensor cores, both maps over one fetch of the values
+                tiles = K.query_tiles(step.host["new_counts"], K.diff_flash_query_tile())
+                K.diff_flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs, tiles, *args)
+            else:
+                K.diff_attention(q, cache.k_pool, cache.v_pool, ctx, cache, *args)
         with phase("o_projection+attention_residual_ms"):
             self.o(ctx, out=residual, accumulate=True)
             if self.o_bias is not None:

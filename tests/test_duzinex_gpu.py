@@ -57,7 +57,7 @@ def model(width, vocab, layers, ffs, loop=None, scale=3.0, eps=1e-5):
 # twice the map size; retention with dim != vdim; a recurrent width other than the feed-forward's; layers without a
 # feed-forward; loops of 1, 2 and 3 passes, over a part or all of the layers, or none
 CONFIGS = {
-    "a": model(64, 200, [att(4, 2, 16, 24, window=20, keep=3, rot=8, cap=5.0), gru(96), ret(3, 8, 16, [0.9, 0.97, 0.5]),
+    "a": model(64, 200, [att(4, 2, 16, 32, window=20, keep=3, rot=8, cap=5.0), gru(96), ret(3, 8, 16, [0.9, 0.97, 0.5]),
                          att(2, 1, 8, 32, window=7, keep=0, rot=8, base=100.0, diff=0.7)],
                [80, None, 48, 72], loop=(1, 3, 3)),
     "b": model(96, 333, [ret(1, 16, 40, [0.99]), att(3, 3, 12, 20, window=70, keep=66, rot=4, cap=None, diff=0.1),
@@ -113,7 +113,8 @@ def _step(lengths, slots=None):
     seq = [b for b, n in enumerate(lengths) for _ in range(n)]
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     return SimpleNamespace(seq_start=i32(starts), seq_slot=i32(slots or list(range(len(lengths)))), token_seq=i32(seq),
-                           n_seqs=len(lengths), all_single=all(n == 1 for n in lengths))
+                           n_seqs=len(lengths), all_single=all(n == 1 for n in lengths), max_new=max(lengths),
+                           host=dict(new_counts=list(lengths)))
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
@@ -174,8 +175,10 @@ def test_token_shift_kernel_carries_the_last_row_in_the_state():
     assert worst(o[0], (a[6] + (a[5] - a[6]) * mu)) <= 1e-6 and torch.equal(state[2].cpu(), a[21])
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(3, 8, 16), (1, 40, 24), (2, 16, 70)])
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 8, 16), (1, 40, 24), (2, 16, 70), (2, 128, 130), (1, 72, 256), (1, 130, 8)])
 def test_retention_kernel(heads, dim, vdim):
+    """Sequences of 50 and 39 tokens run in chunks (where the key size allows), the single token and the portions
+    below token by token; a chunk boundary lies inside nothing here, the next test crosses several."""
     from spissa_b200.csrc import lib as K
     g = torch.Generator().manual_seed(3)
     T, lengths = 90, [50, 1, 39]
@@ -208,6 +211,35 @@ def test_retention_kernel(heads, dim, vdim):
     assert worst(torch.cat(outs[0]), ref[:39]) <= 5e-6 and worst(torch.cat(outs[2]), ref[51:]) <= 5e-6
 
 
+def test_recurrences_in_chunks_agree_with_token_by_token_across_chunk_borders():
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(8)
+    heads, dim, vdim, W = 2, 32, 48, 70
+    lengths = [200, 64, 65, 31]                      # 4 + 1 + 2 chunks, and one sequence below the chunked path's limit
+    T = sum(lengths)
+    proj = torch.randn(T, 2 * heads * dim + 2 * heads * vdim, generator=g).to(DEV)
+    dec = torch.tensor([0.9, 0.999], device=DEV)
+    start = torch.randn(5, heads, dim, vdim, generator=g).to(DEV)          # states that earlier steps left
+    one_by_one = _step(lengths, [4, 1, 0, 2])
+    one_by_one.max_new = 1                                                  # forces the token-by-token kernels
+    s1, s2 = start.clone(), start.clone()
+    o1 = torch.empty(T, heads * vdim, device=DEV)
+    o2 = torch.empty_like(o1)
+    K.retention(proj, s1, dec, o1, one_by_one, heads, dim, vdim, 1e-5)
+    K.retention(proj, s2, dec, o2, _step(lengths, [4, 1, 0, 2]), heads, dim, vdim, 1e-5)
+    assert worst(o2, o1.cpu()) <= 5e-6 and worst(s2, s1.cpu()) <= 5e-6
+    assert torch.equal(s2[3], start[3])                                     # a slot that is not in the step
+    pg = (2 * torch.randn(T, 3 * W, generator=g)).to(DEV)
+    zb, xb = torch.randn(W, generator=g).to(DEV), torch.randn(W, generator=g).to(DEV)
+    g0 = torch.randn(5, W, generator=g).to(DEV)
+    g1, g2 = g0.clone(), g0.clone()
+    y1 = torch.empty(T, W, device=DEV)
+    y2 = torch.empty_like(y1)
+    K.mingru(pg, zb, xb, g1, y1, one_by_one, W)
+    K.mingru(pg, zb, xb, g2, y2, _step(lengths, [4, 1, 0, 2]), W)
+    assert worst(y2, y1.cpu()) <= 2e-6 and worst(g2, g1.cpu()) <= 2e-6
+
+
 def test_mingru_kernel_both_branches_of_the_candidate():
     from spissa_b200.csrc import lib as K
     g = torch.Generator().manual_seed(4)
@@ -226,6 +258,65 @@ def test_mingru_kernel_both_branches_of_the_candidate():
     out = torch.empty(36, W, device=DEV)
     K.mingru(proj.to(DEV), zb.to(DEV), xb.to(DEV), state, out, _step(lengths), W)
     assert worst(out, ref) <= 2e-6
+
+
+@pytest.mark.parametrize("d,vd,H,G", [(16, 16, 2, 2), (32, 64, 4, 1), (64, 128, 2, 1), (128, 32, 1, 1), (128, 128, 2, 2), (24, 40, 2, 1)])
+@pytest.mark.parametrize("window,keep,cap", [(0, 0, 0.0), (50, 0, 4.0), (70, 66, 0.0), (130, 3, 2.0)])
+def test_differential_attention_kernels_over_pages(d, vd, H, G, window, keep, cap):
+    """The prompt kernel on the tensor cores (where its sizes are built) and the kernel for any sizes, in bfloat16 and
+    in 32-bit, against the formula: two sequences in one step, one of which already has 90 keys in the cache, on pages
+    handed out in a scattered order."""
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(d * 1000 + vd + window)
+    new, before = [150, 77], [0, 90]
+    total = [n + b for n, b in zip(new, before)]
+    bf = lambda t: t.to(torch.bfloat16).float()
+    qs = [bf(torch.randn(t, H, 2, d, generator=g)) for t in total]
+    ks = [bf(torch.randn(t, G, 2, d, generator=g)) for t in total]
+    vs = [bf(torch.randn(t, G, vd, generator=g)) for t in total]
+    lam, eps, out_scale, scale = 0.37, 1e-5, 0.8, 1.7 / d ** 0.5
+    refs = []
+    for q, k, v, n in zip(qs, ks, vs, new):
+        q, k, v = q.double(), k.double(), v.double()
+        see = D.visible(q.shape[0], window or None, keep)
+        heads = []
+        for h in range(H):
+            kvh = h // (H // G)
+            maps = []
+            for i in range(2):
+                s = (q[:, h, i] @ k[:, kvh, i].T) * scale
+                if cap:
+                    s = cap * torch.tanh(s / cap)
+                maps.append(torch.softmax(s.masked_fill(~see, float("-inf")), dim=-1) @ v[:, kvh])
+            heads.append(D.unit_rms(maps[0] - lam * maps[1], eps) * out_scale)
+        refs.append(torch.cat(heads, dim=-1)[-n:])
+    ref = torch.cat(refs)
+    n_pages = 8
+    order = [5, 2, 7, 0, 3, 6, 1, 4]
+    table = torch.tensor([order[:3], order[3:6]], dtype=torch.int32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    meta = SimpleNamespace(page_table=table, page_size=64, seq_slot=i32([0, 1]),
+                           token_seq=i32([0] * new[0] + [1] * new[1]),
+                           positions=i32(list(range(before[0], total[0])) + list(range(before[1], total[1]))))
+    q_new = torch.cat([q[-n:] for q, n in zip(qs, new)]).reshape(sum(new), H * 2 * d)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1.5e-2)):
+        kp = torch.zeros(n_pages, G, 64, 2 * d, dtype=dtype, device=DEV)
+        vp = torch.zeros(n_pages, G, 64, vd, dtype=dtype, device=DEV)
+        for b in range(2):
+            for pos in range(total[b]):
+                page = int(table[b, pos // 64])
+                kp[page, :, pos % 64] = ks[b][pos].reshape(G, 2 * d).to(dtype)
+                vp[page, :, pos % 64] = vs[b][pos].to(dtype)
+        qd = q_new.to(dtype).to(DEV)
+        out = torch.empty(sum(new), H * vd, dtype=dtype, device=DEV)
+        K.diff_attention(qd, kp, vp, out, meta, H, G, d, vd, window, keep, scale, cap, lam, eps, out_scale)
+        assert worst(out, ref) <= tol, ("any sizes", dtype)
+        if dtype == torch.bfloat16 and K.diff_flash_supported(d, vd, H, G, 64):
+            fast = torch.empty_like(out)
+            K.diff_flash_prefill(qd, kp, vp, fast, meta, i32([0, new[0], sum(new)]), 2, K.query_tiles(new, 64), H, G, d, vd,
+                                 window, keep, scale, cap, lam, eps, out_scale)
+            assert worst(fast, ref) <= tol, "tensor cores"
+    assert K.diff_flash_supported(d, vd, H, G, 64) == (d in (16, 32, 64, 128) and vd in (16, 32, 64, 128))
 
 
 # ---------------------------------------------------------------------------------------------- whole models
@@ -344,7 +435,7 @@ NEEDLE, DIRECTION = 7, 0
 def needle_model(folder, window, keep, dim=16, rot=8):
     """One attention layer (two heads on one kv head) whose first map gives almost all its weight to the key of token
     ``NEEDLE`` wherever that key is visible, and whose values make the needle's presence large in the logits."""
-    cfg = model(32, 64, [att(2, 1, dim, 12, window=window, keep=keep, rot=rot, cap=30.0, diff=0.2, scale=1.0)], [None], scale=1.0)
+    cfg = model(32, 64, [att(2, 1, dim, 16, window=window, keep=keep, rot=rot, cap=30.0, diff=0.2, scale=1.0)], [None], scale=1.0)
 
     def patch(w):
         w["l0.shift"].zero_()
