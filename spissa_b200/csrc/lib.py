@@ -883,9 +883,9 @@ def retention(proj, state, decay, out, step, H, d, vd, eps):
     if proj.dtype != torch.float32 or state.dtype != torch.float32 or decay.dtype != torch.float32:
         raise KernelError("retention runs on 32-bit projections, state and decays")
     _need_contig(proj, state, decay, out)
+    global launches
     if not step.all_single and step.max_new >= CHUNKED_FROM and retention_chunked_supported(d, vd):
         # a prompt: chunks of 64 tokens in parallel (FFMA tiles), their start states by a short scan
-        global launches
         launches += 3
         n_chunks, T = _chunks(step), proj.shape[0]
         need = lib.sp_retention_chunked_scratch_floats(n_chunks, T, H, d, vd)
@@ -894,6 +894,15 @@ def retention(proj, state, decay, out, step, H, d, vd, eps):
             c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(decay)),
             c_void_p(_ptr(scratch)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)),
             c_void_p(_ptr(step.seq_slot)), step.n_seqs, T, n_chunks, H, d, vd, c_float(eps), c_void_p(_stream())))
+        return
+    if step.all_single and d <= 4096:
+        # a decode step: the states are streamed once, straight from and to global memory
+        launches += 1
+        o_raw = torch.empty(proj.shape[0] * H * vd, dtype=torch.float32, device=proj.device)
+        _check("seqmix", lib.sp_retention_step(
+            c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(decay)),
+            c_void_p(_ptr(o_raw)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)),
+            c_void_p(_ptr(step.seq_slot)), step.n_seqs, H, d, vd, c_float(eps), c_void_p(_stream())))
         return
     _check("seqmix", lib.sp_retention(
         c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(decay)),
@@ -923,7 +932,7 @@ def mingru(proj, z_bias, x_bias, state, out, step, W):
         # a prompt: chunks of 64 tokens in parallel, their start states by a short scan
         global launches
         launches += 2
-        n_chunks = _chunks(step)
+        n_chunks = query_tiles(step.host["new_counts"], int(lib.sp_mingru_chunk_tokens()))
         scratch = torch.empty(n_chunks * W * 2, dtype=torch.float32, device=proj.device)
         _check("seqmix", lib.sp_mingru_chunked(
             c_void_p(_ptr(proj)), c_void_p(_ptr(z_bias)), c_void_p(_ptr(x_bias)), _w_dt(z_bias, x_bias),

@@ -75,6 +75,32 @@ __global__ void token_shift_kernel(ShiftArgs a, int save) {
     if (slot < 0 || slot >= a.n_slots) return;
     const float alpha = DYT ? sp_ld_dt(a.alpha, a.w_dt, 0) : 0.0f;
     float* st = a.state + (size_t)slot * a.H;
+    if (DYT && (a.H & 3) == 0 && ((((uintptr_t)a.x) | ((uintptr_t)a.state) | ((uintptr_t)a.out)) & 15) == 0) {
+        // four neighbouring columns per thread: 16-byte loads of the stream and of the state
+        const float* x = (const float*)a.x;
+        for (int c = threadIdx.x * 4; c < a.H; c += blockDim.x * 4) {
+            const float4 cur = *(const float4*)(x + (size_t)t * a.H + c);
+            const float4 old = first ? *(const float4*)(st + c) : *(const float4*)(x + (size_t)(t - 1) * a.H + c);
+            const float xc[4] = {cur.x, cur.y, cur.z, cur.w}, xo[4] = {old.x, old.y, old.z, old.w};
+            float h[4], o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float w = sp_ld_dt(a.w, a.w_dt, c + i), b = sp_ld_dt(a.b, a.w_dt, c + i);
+                h[i] = tanhf(alpha * xc[i]) * w + b;
+                const float prev = first ? xo[i] : tanhf(alpha * xo[i]) * w + b;
+                o[i] = h[i] + (prev - h[i]) * sp_ld_dt(a.mu, a.mu_dt, c + i);
+            }
+            if (a.out_dt == SP_DT_F32) *(float4*)((float*)a.out + (size_t)t * a.H + c) = make_float4(o[0], o[1], o[2], o[3]);
+            else {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
+                uint2 pk;
+                pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1;
+                *(uint2*)((__nv_bfloat16*)a.out + (size_t)t * a.H + c) = pk;
+            }
+            if (save && last) *(float4*)(st + c) = make_float4(h[0], h[1], h[2], h[3]);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < a.H; c += blockDim.x) {
         const float h = shift_h<DYT>(a, t, c, alpha);
         const float prev = first ? st[c] : shift_h<DYT>(a, t - 1, c, alpha);
@@ -357,6 +383,186 @@ diff_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, co
     }
 }
 
+// The same for steps of few (token, head) pairs over many keys (decoding): eight warps share one pair and take the
+// chunks of 32 visible keys in turn; key and value rows are read in 16- and 8-byte pieces (d a multiple of 8, vd of
+// 4), a lane owns four neighbouring value columns; warp 0 merges the eight parts in warp order.
+#define DD_WARPS 8
+
+__device__ __forceinline__ void dd_ld8(const float* p, float (&v)[8]) {
+    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void dd_ld8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *(const uint4*)p;
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void dd_ld4(const float* p, float (&v)[4]) {
+    const float4 a = *(const float4*)p;
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void dd_ld4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 raw = *(const uint2*)p;
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(DD_WARPS * 32)
+diff_decode_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
+                   TQ* __restrict__ out, KvPlace pl, DiffArgs a) {
+    constexpr int NV = DA_MAX_VD / 128;                      // groups of four columns a lane may own
+    __shared__ __align__(16) float qs[2 * DA_MAX_D];
+    __shared__ __align__(16) float part[DD_WARPS][2][DA_MAX_VD];
+    __shared__ float part_ml[DD_WARPS][4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x / a.H, h = blockIdx.x % a.H;
+    const int g = h / (a.H / a.G);
+    const int d = a.d, vd = a.vd, kd = 2 * a.d;
+    const int p = pl.positions[t];
+    const int row = sp_checked_row(pl.seq_slot[pl.token_seq[t]], pl.rg);
+    const int* pt = pl.page_table + (size_t)row * pl.max_pages;
+    const int ps = pl.page_size;
+    for (int c = threadIdx.x; c < kd; c += blockDim.x) qs[c] = sp_ld(q, ((size_t)t * a.H + h) * kd + c);
+    __syncthreads();
+
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    const int n_first = a.keep_first < lo ? a.keep_first : lo;
+    const int n_vis = n_first + (p - lo + 1);
+    float m1 = -INFINITY, l1 = 0.0f, m2 = -INFINITY, l2 = 0.0f;
+    float acc1[NV][4], acc2[NV][4];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc1[i][u] = acc2[i][u] = 0.0f;
+
+    for (int v0 = 32 * warp; v0 < n_vis; v0 += 32 * DD_WARPS) {
+        const int vi = v0 + lane;
+        const bool valid = vi < n_vis;
+        float s1 = -INFINITY, s2 = -INFINITY;
+        int my_page = 0, my_off = 0;
+        if (valid) {
+            const int j = vi < n_first ? vi : lo + (vi - n_first);
+            my_page = sp_checked_page(pt[sp_checked_entry(j / ps, pl.max_pages, pl.rg)], pl.rg);
+            my_off = j % ps;
+            const TC* kr = kpool + (((size_t)my_page * a.G + g) * ps + my_off) * kd;
+            float d1 = 0.0f, d2 = 0.0f;
+            for (int c = 0; c < d; c += 8) {
+                float k1[8], k2[8];
+                dd_ld8(kr + c, k1);
+                dd_ld8(kr + d + c, k2);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { d1 = fmaf(qs[c + u], k1[u], d1); d2 = fmaf(qs[d + c + u], k2[u], d2); }
+            }
+            s1 = d1 * a.scale;
+            s2 = d2 * a.scale;
+            if (a.softcap > 0.0f) {
+                s1 = a.softcap * tanhf(s1 / a.softcap);
+                s2 = a.softcap * tanhf(s2 / a.softcap);
+            }
+        }
+        const float n1 = fmaxf(m1, sp_warp_max(s1)), n2 = fmaxf(m2, sp_warp_max(s2));
+        const float e1 = valid ? expf(s1 - n1) : 0.0f, e2 = valid ? expf(s2 - n2) : 0.0f;
+        const float c1 = expf(m1 - n1), c2 = expf(m2 - n2);
+        l1 = l1 * c1 + sp_warp_sum(e1);
+        l2 = l2 * c2 + sp_warp_sum(e2);
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { acc1[i][u] *= c1; acc2[i][u] *= c2; }
+        const int n_valid = min(32, n_vis - v0);
+        for (int jj0 = 0; jj0 < n_valid; jj0 += 8) {
+            float w1[8], w2[8];
+            const TC* vr[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                w1[u] = __shfl_sync(0xffffffffu, e1, (jj0 + u) & 31);      // lanes beyond n_valid hold weight 0
+                w2[u] = __shfl_sync(0xffffffffu, e2, (jj0 + u) & 31);
+                const int pg = __shfl_sync(0xffffffffu, my_page, (jj0 + u) & 31);
+                const int of = __shfl_sync(0xffffffffu, my_off, (jj0 + u) & 31);
+                vr[u] = vpool + (((size_t)pg * a.G + g) * ps + of) * vd;   // page 0, offset 0 for those lanes: readable
+            }
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int c = 4 * lane + 128 * i;
+                if (c < vd) {
+                    float v[8][4];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) dd_ld4(vr[u] + c, v[u]);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            acc1[i][x] = fmaf(w1[u], v[u][x], acc1[i][x]);
+                            acc2[i][x] = fmaf(w2[u], v[u][x], acc2[i][x]);
+                        }
+                }
+            }
+        }
+        m1 = n1;
+        m2 = n2;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = 4 * lane + 128 * i;
+        if (c < vd) {
+            *(float4*)&part[warp][0][c] = make_float4(acc1[i][0], acc1[i][1], acc1[i][2], acc1[i][3]);
+            *(float4*)&part[warp][1][c] = make_float4(acc2[i][0], acc2[i][1], acc2[i][2], acc2[i][3]);
+        }
+    }
+    if (lane == 0) { part_ml[warp][0] = m1; part_ml[warp][1] = l1; part_ml[warp][2] = m2; part_ml[warp][3] = l2; }
+    __syncthreads();
+    if (warp != 0) return;
+    float mm1 = -INFINITY, mm2 = -INFINITY;
+    for (int w = 0; w < DD_WARPS; ++w) { mm1 = fmaxf(mm1, part_ml[w][0]); mm2 = fmaxf(mm2, part_ml[w][2]); }
+    l1 = l2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc1[i][u] = acc2[i][u] = 0.0f;
+    for (int w = 0; w < DD_WARPS; ++w) {
+        if (part_ml[w][1] <= 0.0f) continue;                     // a warp that saw no key
+        const float f1 = expf(part_ml[w][0] - mm1), f2 = expf(part_ml[w][2] - mm2);
+        l1 += part_ml[w][1] * f1;
+        l2 += part_ml[w][3] * f2;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = 4 * lane + 128 * i;
+            if (c < vd) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    acc1[i][u] = fmaf(part[w][0][c + u], f1, acc1[i][u]);
+                    acc2[i][u] = fmaf(part[w][1][c + u], f2, acc2[i][u]);
+                }
+            }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = 4 * lane + 128 * i;
+        if (c < vd) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                acc1[i][u] = acc1[i][u] / l1 - a.lam * (acc2[i][u] / l2);
+                ss = fmaf(acc1[i][u], acc1[i][u], ss);
+            }
+        }
+    }
+    ss = sp_warp_sum(ss);
+    const float inv = a.out_scale / sqrtf(ss / (float)vd + a.eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = 4 * lane + 128 * i;
+        if (c < vd) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) sp_st(out, ((size_t)t * a.H + h) * vd + c + u, acc1[i][u] * inv);
+        }
+    }
+}
+
 SP_API int sp_diff_attention(const void* q, int q_dt, const void* kpool, const void* vpool, int cache_dt, void* out,
                              const int* token_seq, const int* positions, const int* seq_slot, const int* page_table,
                              int max_pages, int page_size, int T, int H, int G, int d, int vd, int window, int keep_first,
@@ -371,6 +577,20 @@ SP_API int sp_diff_attention(const void* q, int q_dt, const void* kpool, const v
     const bool split = warps <= 2048;
     const long long blocks = split ? warps : (warps + DA_WARPS - 1) / DA_WARPS;
     if (blocks > 2147483647LL) SP_FAIL("diff_attention: too many (token, head) pairs for one launch");
+    const size_t esz = cache_dt == SP_DT_F32 ? 4 : 2;
+    if (split && d % 8 == 0 && vd % 4 == 0 && (((uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0 && ((size_t)vd * esz) % 8 == 0) {
+#define DD_LAUNCH(TQ, TC)                                                                                             \
+        diff_decode_kernel<TQ, TC><<<(unsigned)blocks, DD_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool,    \
+                                                                                   (const TC*)vpool, (TQ*)out, pl, a)
+        if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) DD_LAUNCH(float, float);
+        else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) DD_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+        else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) DD_LAUNCH(float, __nv_bfloat16);
+        else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_F32) DD_LAUNCH(__nv_bfloat16, float);
+        else SP_FAIL("diff_attention: unsupported dtype codes %d/%d", q_dt, cache_dt);
+#undef DD_LAUNCH
+        SP_CHECK_LAUNCH("diff_decode");
+        return 0;
+    }
 #define DA_LAUNCH(TQ, TC)                                                                                             \
     do {                                                                                                              \
         if (split) diff_attention_kernel<TQ, TC, true><<<(unsigned)blocks, DA_WARPS * 32, 0, stream>>>(               \
@@ -493,6 +713,7 @@ SP_API int sp_retention(const float* proj, int ld, float* state, int n_slots, co
 // All products are tiles of out[m][n] = Σ_k a[k][m]·b[k][n] with a and b in shared memory, k-major, 16 x 16 threads
 // owning 4·MA x 4·NB outputs each.
 #define RC_CHUNK 64
+#define RC_TS 68               // row stride of the transposed 64-token arrays
 
 template <int MA, int NB>
 __device__ __forceinline__ void rc_mm(const float* __restrict__ a, int lda, const float* __restrict__ b, int ldb, int K,
@@ -552,14 +773,17 @@ __global__ void __launch_bounds__(256) retention_chunk_sum_kernel(RcArgs a) {
     const int DP = 64 * MA, NP = 64 * NB;
     float* kd = sm;                    // [64][DP]   γ^{n−1−j} k_j / √d
     float* vv = kd + RC_CHUNK * DP;    // [64][NP]
+    __shared__ float pw[RC_CHUNK + 1];
     int s, t0, n;
     if (!rc_chunk_of(a, blockIdx.x, s, t0, n)) return;
     const int h = blockIdx.y, c0 = blockIdx.z * NP;
     const int d = a.d, vd = a.vd, Hd = a.H * d;
     const float gamma = a.decay[h], kscale = 1.0f / sqrtf((float)d);
+    if (threadIdx.x <= RC_CHUNK) pw[threadIdx.x] = powf(gamma, (float)threadIdx.x);
+    __syncthreads();
     for (int e = threadIdx.x; e < RC_CHUNK * DP; e += 256) {
         const int j = e / DP, i = e - j * DP;
-        kd[e] = (j < n && i < d) ? a.proj[(size_t)(t0 + j) * a.ld + Hd + h * d + i] * kscale * powf(gamma, (float)(n - 1 - j)) : 0.0f;
+        kd[e] = (j < n && i < d) ? a.proj[(size_t)(t0 + j) * a.ld + Hd + h * d + i] * kscale * pw[n - 1 - j] : 0.0f;
     }
     for (int e = threadIdx.x; e < RC_CHUNK * NP; e += 256) {
         const int j = e / NP, c = e - j * NP;
@@ -585,27 +809,48 @@ __global__ void __launch_bounds__(256) retention_chunk_sum_kernel(RcArgs a) {
     }
 }
 
-// (B) grid (B, H, pieces of d·vd)
+// (B) grid (B, H, pieces of d·vd): VEC elements per thread, the loads of four chunks in flight at a time
+template <int VEC>
 __global__ void retention_chunk_scan_kernel(RcArgs a) {
     const int s = blockIdx.x, h = blockIdx.y;
     const int slot = a.seq_slot[s];
     if (slot < 0 || slot >= a.n_slots) return;
-    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int e = (blockIdx.z * blockDim.x + threadIdx.x) * VEC;
     if (e >= a.d * a.vd) return;
     int c = 0;                                              // the sequence's first chunk among all chunks of the step
     for (int b = 0; b < s; ++b) c += (a.seq_start[b + 1] - a.seq_start[b] + RC_CHUNK - 1) / RC_CHUNK;
     const int cnt = a.seq_start[s + 1] - a.seq_start[s];
+    const int n_chunks = (cnt + RC_CHUNK - 1) / RC_CHUNK;
     const float gamma = a.decay[h];
+    const float g_full = powf(gamma, (float)RC_CHUNK), g_last = powf(gamma, (float)(cnt - (n_chunks - 1) * RC_CHUNK));
+    const size_t stride = (size_t)a.H * a.d * a.vd;
     float* gS = a.state + ((size_t)slot * a.H + h) * a.d * a.vd + e;
-    float S = *gS;
-    for (int x = 0; x * RC_CHUNK < cnt; ++x, ++c) {
-        const int n = min(RC_CHUNK, cnt - x * RC_CHUNK);
-        float* p = a.chunk_state + ((size_t)c * a.H + h) * a.d * a.vd + e;
-        const float own = *p;
-        *p = S;
-        S = fmaf(powf(gamma, (float)n), S, own);
+    float* p = a.chunk_state + ((size_t)c * a.H + h) * a.d * a.vd + e;
+    float S[VEC];
+    if (VEC == 4) { const float4 v = *(const float4*)gS; S[0] = v.x; S[1] = v.y; S[2] = v.z; S[3] = v.w; }
+    else S[0] = *gS;
+    for (int x0 = 0; x0 < n_chunks; x0 += 4) {
+        float own[4][VEC];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (x0 + u >= n_chunks) break;
+            if (VEC == 4) {
+                const float4 v = *(const float4*)(p + (size_t)(x0 + u) * stride);
+                own[u][0] = v.x; own[u][1] = v.y; own[u][2] = v.z; own[u][3] = v.w;
+            } else own[u][0] = p[(size_t)(x0 + u) * stride];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (x0 + u >= n_chunks) break;
+            if (VEC == 4) *(float4*)(p + (size_t)(x0 + u) * stride) = make_float4(S[0], S[1], S[2], S[3]);
+            else p[(size_t)(x0 + u) * stride] = S[0];
+            const float gn = x0 + u == n_chunks - 1 ? g_last : g_full;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) S[i] = fmaf(gn, S[i], own[u][i]);
+        }
     }
-    *gS = S;
+    if (VEC == 4) *(float4*)gS = make_float4(S[0], S[1], S[2], S[3]);
+    else *gS = S[0];
 }
 
 // (C) grid (chunks, H, column blocks of 64·NB); MA = ceil(d / 64) sizes the shared arrays only
@@ -613,9 +858,9 @@ template <int NB>
 __global__ void __launch_bounds__(256) retention_chunk_out_kernel(RcArgs a, int DP) {
     extern __shared__ __align__(16) float sm[];
     const int NP = 64 * NB;
-    float* qT = sm;                         // [DP][64]
-    float* kT = qT + (size_t)DP * 64;       // [DP][64]   k / √d
-    float* S = kT + (size_t)DP * 64;        // [DP][NP]
+    float* qT = sm;                         // [DP][RC_TS]  (rows padded: the transposed stores then spread over the banks)
+    float* kT = qT + (size_t)DP * RC_TS;    // [DP][RC_TS]  k / √d
+    float* S = kT + (size_t)DP * RC_TS;     // [DP][NP]
     float* vv = S + (size_t)DP * NP;        // [64][NP]
     float* pT = vv + 64 * NP;               // [64 keys][64 queries]
     __shared__ float pw[RC_CHUNK + 1];
@@ -629,8 +874,8 @@ __global__ void __launch_bounds__(256) retention_chunk_out_kernel(RcArgs a, int 
         const int j = e / DP, i = e - j * DP;               // token j, dim i: read along the dims, store transposed
         const bool ok = j < n && i < d;
         const float* row = a.proj + (size_t)(t0 + j) * a.ld;
-        qT[i * 64 + j] = ok ? row[h * d + i] : 0.0f;
-        kT[i * 64 + j] = ok ? row[Hd + h * d + i] * kscale : 0.0f;
+        qT[i * RC_TS + j] = ok ? row[h * d + i] : 0.0f;
+        kT[i * RC_TS + j] = ok ? row[Hd + h * d + i] * kscale : 0.0f;
     }
     const float* gS = a.chunk_state + ((size_t)blockIdx.x * a.H + h) * d * vd;
     for (int e = threadIdx.x; e < DP * NP; e += 256) {
@@ -644,20 +889,24 @@ __global__ void __launch_bounds__(256) retention_chunk_out_kernel(RcArgs a, int 
     __syncthreads();
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     {
-        // P[i][j] = γ^{i−j} q_i · k_j for j ≤ i, stored as pT[j][i]
+        // pT[j][i] = γ^{i−j} q_i · k_j for j ≤ i (keys as the rows of the product, so that a thread stores whole float4)
         float p[4][4];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
 #pragma unroll
             for (int v = 0; v < 4; ++v) p[u][v] = 0.0f;
-        rc_mm<1, 1>(qT, 64, kT, 64, d, p, ty, tx);
+        rc_mm<1, 1>(kT, RC_TS, qT, RC_TS, d, p, ty, tx);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 4; ++u) {
+            const int j = 4 * ty + u;
+            float r[4];
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-                const int i = 4 * ty + u, j = 4 * tx + v;
-                pT[j * 64 + i] = (j <= i && i < n) ? p[u][v] * pw[i - j] : 0.0f;
+                const int i = 4 * tx + v;
+                r[v] = (j <= i && i < n) ? p[u][v] * pw[i - j] : 0.0f;
             }
+            *(float4*)(pT + j * 64 + 4 * tx) = make_float4(r[0], r[1], r[2], r[3]);
+        }
     }
     __syncthreads();
     float inter[4][4 * NB], intra[4][4 * NB];
@@ -665,7 +914,7 @@ __global__ void __launch_bounds__(256) retention_chunk_out_kernel(RcArgs a, int 
     for (int u = 0; u < 4; ++u)
 #pragma unroll
         for (int v = 0; v < 4 * NB; ++v) inter[u][v] = intra[u][v] = 0.0f;
-    rc_mm<1, NB>(qT, 64, S, NP, d, inter, ty, tx);
+    rc_mm<1, NB>(qT, RC_TS, S, NP, d, inter, ty, tx);
     rc_mm<1, NB>(pT, 64, vv, NP, n, intra, ty, tx);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -712,7 +961,7 @@ SP_API int sp_retention_chunked(const float* proj, int ld, float* state, int n_s
     const int DP = 64 * MA, NP = 64 * NB;
     const dim3 grid(n_chunks, H, (vd + NP - 1) / NP);
     const size_t smem_a = (size_t)(RC_CHUNK * DP + RC_CHUNK * NP) * sizeof(float);
-    const size_t smem_c = ((size_t)2 * DP * 64 + (size_t)DP * NP + 64 * NP + 64 * 64) * sizeof(float);
+    const size_t smem_c = ((size_t)2 * DP * RC_TS + (size_t)DP * NP + 64 * NP + 64 * 64) * sizeof(float);
     static SpPerDevice ready;
     if (!ready.done()) {
         const int big = 200 * 1024;
@@ -730,12 +979,79 @@ SP_API int sp_retention_chunked(const float* proj, int ld, float* state, int n_s
     else if (NB == 1) retention_chunk_sum_kernel<2, 1><<<grid, 256, smem_a, stream>>>(a);
     else retention_chunk_sum_kernel<2, 2><<<grid, 256, smem_a, stream>>>(a);
     SP_CHECK_LAUNCH("retention_chunk_sum");
-    retention_chunk_scan_kernel<<<dim3(B, H, (d * vd + 255) / 256), 256, 0, stream>>>(a);
+    if (vd % 4 == 0 && (((uintptr_t)state | (uintptr_t)scratch) & 15) == 0)
+        retention_chunk_scan_kernel<4><<<dim3(B, H, (d * vd / 4 + 127) / 128), 128, 0, stream>>>(a);
+    else
+        retention_chunk_scan_kernel<1><<<dim3(B, H, (d * vd + 255) / 256), 256, 0, stream>>>(a);
     SP_CHECK_LAUNCH("retention_chunk_scan");
     if (NB == 1) retention_chunk_out_kernel<1><<<grid, 256, smem_c, stream>>>(a, DP);
     else retention_chunk_out_kernel<2><<<grid, 256, smem_c, stream>>>(a, DP);
     SP_CHECK_LAUNCH("retention_chunk_out");
     retention_finish_kernel<<<dim3(T, H), 128, 0, stream>>>(a, T);
+    SP_CHECK_LAUNCH("retention_finish");
+    return 0;
+}
+
+// ============================================================== retention of a decode step (one token per sequence)
+// The state is streamed once: grid (sequences, heads, blocks of 32 value columns), thread (j, y) takes column j of
+// the rows i ≡ y (mod 8) straight from and to global memory; the eight partial sums of a column are added in the
+// order of y. The unit rms over all of a head's columns and the gate follow in ``retention_finish_kernel``.
+__global__ void __launch_bounds__(256) retention_step_kernel(RcArgs a) {
+    extern __shared__ float sm[];
+    float* qk = sm;                        // q [d], k/√d [d]
+    float* red = qk + 2 * a.d;             // [8][32]
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int t = a.seq_start[s];
+    const int d = a.d, vd = a.vd, Hd = a.H * d;
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    const int j = blockIdx.z * 32 + x;
+    const float* row = a.proj + (size_t)t * a.ld;
+    const float kscale = 1.0f / sqrtf((float)d), gamma = a.decay[h];
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+        qk[e] = row[h * d + e];
+        qk[d + e] = row[Hd + h * d + e] * kscale;
+    }
+    __syncthreads();
+    float part = 0.0f;
+    if (j < vd) {
+        const float v = row[2 * Hd + h * vd + j];
+        float* gS = a.state + ((size_t)slot * a.H + h) * d * vd + j;
+        for (int i0 = y; i0 < d; i0 += 32) {
+            float st[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) st[u] = i0 + 8 * u < d ? gS[(size_t)(i0 + 8 * u) * vd] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + 8 * u;
+                if (i >= d) break;
+                const float sv = fmaf(gamma, st[u], qk[d + i] * v);
+                gS[(size_t)i * vd] = sv;
+                part = fmaf(sv, qk[i], part);
+            }
+        }
+    }
+    red[y * 32 + x] = part;
+    __syncthreads();
+    if (y == 0 && j < vd) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int yy = 0; yy < 8; ++yy) sum += red[yy * 32 + x];
+        a.o_raw[(size_t)t * a.H * vd + h * vd + j] = sum;
+    }
+}
+
+SP_API int sp_retention_step(const float* proj, int ld, float* state, int n_slots, const float* decay, float* o_raw,
+                             void* out, int out_dt, const int* seq_start, const int* seq_slot, int B, int H, int d, int vd,
+                             float eps, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    RcArgs a{proj, ld, state, decay, nullptr, o_raw, out, out_dt, seq_start, seq_slot, B, H, d, vd, n_slots, 0, eps};
+    const size_t smem = ((size_t)2 * d + 256) * sizeof(float);
+    if (smem > 48 * 1024) SP_FAIL("retention (step): key size %d is beyond this kernel's range", d);
+    retention_step_kernel<<<dim3(B, H, (vd + 31) / 32), 256, smem, stream>>>(a);
+    SP_CHECK_LAUNCH("retention_step");
+    retention_finish_kernel<<<dim3(B, H), 128, 0, stream>>>(a, B);
     SP_CHECK_LAUNCH("retention_finish");
     return 0;
 }
@@ -773,11 +1089,11 @@ SP_API int sp_mingru(const float* proj, const void* zb, const void* xb, int b_dt
     return 0;
 }
 
-// ============================================================== minGRU of a prompt step, in chunks of 64 tokens
+// ============================================================== minGRU of a prompt step, in chunks of 32 tokens
 // S_t = a_t S_{t-1} + b_t with a_t = 1 − z_t, b_t = z_t c_t composes: over a chunk S_end = A·S_start + Bsum with
 // A = Π a_t and Bsum the chunk run from zero. (1) every (chunk, channel) finds (A, Bsum); (2) per (sequence, channel)
 // the chunks' start states one after the other; (3) every (chunk, channel) runs again from its start state and writes.
-#define MG_CHUNK 64
+#define MG_CHUNK 32
 
 __device__ __forceinline__ bool mg_chunk_of(const int* seq_start, int B, int x, int& s, int& t0, int& n) {
     for (s = 0; s < B; ++s) {
@@ -804,14 +1120,26 @@ __global__ void mingru_chunk_kernel(const float* __restrict__ proj, const void* 
     const float bz = sp_ld_dt(zb, b_dt, c), bx = sp_ld_dt(xb, b_dt, c);
     float2* cell = scratch + (size_t)blockIdx.y * W + c;
     float S = PASS == 1 ? 0.0f : cell->x, A = 1.0f;
-    for (int t = t0; t < t0 + n; ++t) {
-        const float* row = proj + (size_t)t * 3 * W;
-        const float z = sm_sigmoid(row[c] + bz);
-        const float u = row[W + c] + bx;
-        const float cand = u >= 0.0f ? u + 0.5f : sm_sigmoid(u);
-        S = (1.0f - z) * S + z * cand;
-        if (PASS == 1) A *= 1.0f - z;
-        else sp_st_dt(out, out_dt, (size_t)t * W + c, S * sm_silu(row[2 * W + c]));
+    for (int tb = t0; tb < t0 + n; tb += 4) {
+        float pz[4], px[4], pg[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {                        // four tokens' loads in flight
+            const bool in = tb + i < t0 + n;
+            const float* row = proj + (size_t)(in ? tb + i : tb) * 3 * W;
+            pz[i] = row[c];
+            px[i] = row[W + c];
+            pg[i] = PASS == 1 ? 0.0f : row[2 * W + c];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (tb + i >= t0 + n) break;
+            const float z = sm_sigmoid(pz[i] + bz);
+            const float u = px[i] + bx;
+            const float cand = u >= 0.0f ? u + 0.5f : sm_sigmoid(u);
+            S = (1.0f - z) * S + z * cand;
+            if (PASS == 1) A *= 1.0f - z;
+            else sp_st_dt(out, out_dt, (size_t)(tb + i) * W + c, S * sm_silu(pg[i]));
+        }
     }
     if (PASS == 1) *cell = make_float2(A, S);
 }
@@ -835,6 +1163,8 @@ __global__ void mingru_chunk_scan_kernel(float2* __restrict__ scratch, float* __
     }
     state[(size_t)slot * W + c] = S;
 }
+
+SP_API int sp_mingru_chunk_tokens() { return MG_CHUNK; }
 
 SP_API int sp_mingru_chunked(const float* proj, const void* zb, const void* xb, int b_dt, float* state, int n_slots,
                              float* scratch, void* out, int out_dt, const int* seq_start, const int* seq_slot, int B,
@@ -862,6 +1192,20 @@ polynorm_kernel(const float* __restrict__ z, const void* __restrict__ coef, int 
     if (t >= T) return;
     const float* row = z + (size_t)t * F;
     float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    const bool vec = (F & 3) == 0 && (((uintptr_t)z) & 15) == 0;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < F; c += blockDim.x * 4) {
+            const float4 q = *(const float4*)(row + c);
+            const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float v = e[i], v2 = v * v, v3 = v2 * v;
+                s2 = fmaf(v, v, s2);
+                s4 = fmaf(v2, v2, s4);
+                s6 = fmaf(v3, v3, s6);
+            }
+        }
+    } else
     for (int c = threadIdx.x; c < F; c += blockDim.x) {
         const float v = row[c], v2 = v * v, v3 = v2 * v;
         s2 = fmaf(v, v, s2);
@@ -873,6 +1217,26 @@ polynorm_kernel(const float* __restrict__ z, const void* __restrict__ coef, int 
     s6 = sp_block_sum(s6, scratch);
     const float r1 = 1.0f / sqrtf(s2 / (float)F + eps), r2 = 1.0f / sqrtf(s4 / (float)F + eps), r3 = 1.0f / sqrtf(s6 / (float)F + eps);
     const float ca = sp_ld_dt(coef, c_dt, 0), cb = sp_ld_dt(coef, c_dt, 1), cc = sp_ld_dt(coef, c_dt, 2), ce = sp_ld_dt(coef, c_dt, 3);
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < F; c += blockDim.x * 4) {
+            const float4 q = *(const float4*)(row + c);
+            const float e[4] = {q.x, q.y, q.z, q.w};
+            float o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float v = e[i], v2 = v * v, v3 = v2 * v;
+                o[i] = ca * (v * r1) + cb * (v2 * r2) + cc * (v3 * r3) + ce;
+            }
+            if (out_dt == SP_DT_F32) *(float4*)((float*)out + (size_t)t * F + c) = make_float4(o[0], o[1], o[2], o[3]);
+            else {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
+                uint2 pk;
+                pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1;
+                *(uint2*)((__nv_bfloat16*)out + (size_t)t * F + c) = pk;
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < F; c += blockDim.x) {
         const float v = row[c], v2 = v * v, v3 = v2 * v;
         sp_st_dt(out, out_dt, (size_t)t * F + c, ca * (v * r1) + cb * (v2 * r2) + cc * (v3 * r3) + ce);

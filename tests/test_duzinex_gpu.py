@@ -260,11 +260,13 @@ def test_mingru_kernel_both_branches_of_the_candidate():
     assert worst(out, ref) <= 2e-6
 
 
-@pytest.mark.parametrize("d,vd,H,G", [(16, 16, 2, 2), (32, 64, 4, 1), (64, 128, 2, 1), (128, 32, 1, 1), (128, 128, 2, 2), (24, 40, 2, 1)])
+@pytest.mark.parametrize("d,vd,H,G", [(16, 16, 2, 2), (32, 64, 4, 1), (64, 128, 2, 1), (128, 32, 1, 1), (128, 128, 2, 2), (24, 40, 2, 1),
+                                      (12, 20, 3, 3), (16, 20, 16, 4)])
 @pytest.mark.parametrize("window,keep,cap", [(0, 0, 0.0), (50, 0, 4.0), (70, 66, 0.0), (130, 3, 2.0)])
 def test_differential_attention_kernels_over_pages(d, vd, H, G, window, keep, cap):
-    """The prompt kernel on the tensor cores (where its sizes are built) and the kernel for any sizes, in bfloat16 and
-    in 32-bit, against the formula: two sequences in one step, one of which already has 90 keys in the cache, on pages
+    """The prompt kernel on the tensor cores (where its sizes are built) and the kernels for any sizes (one warp per
+    (token, head) for many pairs; for few pairs the warps of a CTA sharing the keys, with wide loads where the sizes
+    allow), in bfloat16 and in 32-bit, against the formula: two sequences in one step, one of which already has 90 keys in the cache, on pages
     handed out in a scattered order."""
     from spissa_b200.csrc import lib as K
     g = torch.Generator().manual_seed(d * 1000 + vd + window)
