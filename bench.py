@@ -580,6 +580,69 @@ def kernel_case(name: str, reps: int) -> int:
             run = lambda i: K.flash_decode(q, pools[i % n_buf][0], pools[i % n_buf][1], out, meta, seq_len, nh, nkv,
                                            hd, None, scale, ct, nc, scratch)
             bytes_ = B * T * nkv * hd * 2 * 2.0
+    elif name in ("diff_flash", "diff_decode"):
+        # the Duzinex attention at the 2k size of --design: 16 heads on 4 kv heads, maps of 64, values of 128, window 1,024
+        # with 4 kept tokens, cap 30; a 2,048-token prompt, or one query each of 8 sequences with 2,048 cached tokens
+        Hq, G, d, vd, win, keep = 16, 4, 64, 128, 1024, 4
+        B = 8 if name == "diff_decode" else 1
+        n_new = 1 if name == "diff_decode" else T
+        pages = B * (T // 64)
+        n_buf = 12 if name == "diff_decode" else 1
+        pools = [(rnd(pages, G, 64, 2 * d), rnd(pages, G, 64, vd)) for _ in range(n_buf)]
+        ar = torch.arange(B, dtype=torch.int32, device=dev)
+        meta = SimpleNamespace(page_table=torch.arange(pages, dtype=torch.int32, device=dev).view(B, T // 64), page_size=64,
+                               seq_slot=ar, positions=(torch.arange(n_new, dtype=torch.int32, device=dev) + (T - n_new)).repeat(B),
+                               token_seq=ar.repeat_interleave(n_new))
+        q = rnd(B * n_new, Hq * 2 * d)
+        out = torch.empty(B * n_new, Hq * vd, dtype=bf, device=dev)
+        consts = (Hq, G, d, vd, win, keep, d ** -0.5, 30.0, 0.4, 1e-6, 0.5)
+        if name == "diff_flash":
+            seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+            run = lambda i: K.diff_flash_prefill(q, pools[0][0], pools[0][1], out, meta, seq_start, 1, T // 64, *consts)
+            flops = (T * win - win * (win - 1) / 2) * Hq * (4.0 * d + 4.0 * vd)
+        else:
+            run = lambda i: K.diff_attention(q, pools[i % n_buf][0], pools[i % n_buf][1], out, meta, *consts)
+            bytes_ = B * (win + keep) * G * (2 * d + vd) * 2.0
+    elif name in ("retention_chunks", "retention_step", "mingru_chunks", "polynorm", "token_shift"):
+        # the other Duzinex kernels at the 2k size of --design (8 retention heads of 128 x 256, width 2,048, ff 8,192)
+        rh, rd, rvd, Wd, ff = 8, 128, 256, 2048, 8192
+        B = 8 if name == "retention_step" else 1
+        n_new = 1 if B > 1 else T
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        step = SimpleNamespace(seq_start=i32([n_new * b for b in range(B + 1)]), seq_slot=i32(list(range(B))),
+                               token_seq=torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(n_new), n_seqs=B,
+                               all_single=n_new == 1, max_new=n_new, host=dict(new_counts=[n_new] * B))
+        if name.startswith("retention"):
+            n_buf = 6 if B > 1 else 1
+            proj = torch.randn(B * n_new, 2 * rh * rd + 2 * rh * rvd, device=dev)
+            states = [torch.zeros(B, rh, rd, rvd, device=dev) for _ in range(n_buf)]
+            decay = torch.full((rh,), 0.97, device=dev)
+            out = torch.empty(B * n_new, rh * rvd, dtype=bf, device=dev)
+            run = lambda i: K.retention(proj, states[i % n_buf], decay, out, step, rh, rd, rvd, 1e-6)
+            if B > 1:
+                bytes_ = B * rh * rd * rvd * 4 * 2.0
+            else:
+                flops = T * rh * 4.0 * rd * rvd              # the recurrence's own FLOPs (the chunked form does six times as many)
+        elif name == "mingru_chunks":
+            proj = torch.randn(T, 3 * Wd, device=dev)
+            zb, xb = rnd(Wd), rnd(Wd)
+            state = torch.zeros(1, Wd, device=dev)
+            out = torch.empty(T, Wd, dtype=bf, device=dev)
+            run = lambda i: K.mingru(proj, zb, xb, state, out, step, Wd)
+            bytes_ = T * Wd * (2 * 3 * 4 + 2.0)
+        elif name == "polynorm":
+            zs = [torch.randn(T, ff, device=dev) for _ in range(3)]
+            coef = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev).to(bf)
+            out = torch.empty(T, ff, dtype=bf, device=dev)
+            run = lambda i: K.polynorm(zs[i % 3], coef, out, 1e-6)
+            bytes_ = T * ff * (4 + 2.0)
+        else:
+            xs = [torch.randn(T, Wd, device=dev) for _ in range(6)]
+            w, b, al, mu = rnd(Wd), rnd(Wd), torch.full((1,), 0.5, device=dev).to(bf), rnd(Wd)
+            state = torch.zeros(1, Wd, device=dev)
+            out = torch.empty(T, Wd, dtype=bf, device=dev)
+            run = lambda i: K.token_shift(xs[i % 6], mu, state, out, step, dyt=(w, b, al))
+            bytes_ = T * Wd * (4 + 2.0)
     elif name in ("sample_b8", "sample_b64", "argmax_b8"):
         # the sampler on rows of 128,256 logits (standard deviation 4 after the temperature): temperature 0.8, top-p 0.95
         B = 64 if name.endswith("b64") else 8
@@ -641,7 +704,7 @@ def main() -> int:
                     help="add per-phase timings of one prompt step and of part-by-part decode steps")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
+                         "gemv_down|gemv_head|diff_flash|diff_decode|retention_chunks|retention_step|mingru_chunks|polynorm|token_shift|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
     ap.add_argument("--design", default=None, choices=["duzinex"],
                     help="measure this design beside the Llama decoder at equal layer sizes instead of the headline workload")
     ap.add_argument("--design-sizes", default="", dest="design_sizes", help="which of 1k,2k,4k (default: all)")

@@ -837,7 +837,7 @@ def token_shift(x, mu, state, out, step, dyt=None):
         raise KernelError("token_shift keeps a float32 state of the stream's width per slot")
     w, b, a = dyt if dyt is not None else (None, None, None)
     global launches
-    if not step.all_single:
+    if not step.all_single and (dyt is None or H % 4):
         launches += 1                                  # the state is stored by a second launch behind the first
     _check("seqmix", lib.sp_token_shift(
         c_void_p(_ptr(x)), dt_code(x), c_void_p(_ptr(w)), c_void_p(_ptr(b)), c_void_p(_ptr(a)),

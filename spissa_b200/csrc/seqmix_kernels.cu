@@ -75,21 +75,67 @@ __global__ void token_shift_kernel(ShiftArgs a, int save) {
     if (slot < 0 || slot >= a.n_slots) return;
     const float alpha = DYT ? sp_ld_dt(a.alpha, a.w_dt, 0) : 0.0f;
     float* st = a.state + (size_t)slot * a.H;
-    if (DYT && (a.H & 3) == 0 && ((((uintptr_t)a.x) | ((uintptr_t)a.state) | ((uintptr_t)a.out)) & 15) == 0) {
-        // four neighbouring columns per thread: 16-byte loads of the stream and of the state
-        const float* x = (const float*)a.x;
-        for (int c = threadIdx.x * 4; c < a.H; c += blockDim.x * 4) {
-            const float4 cur = *(const float4*)(x + (size_t)t * a.H + c);
-            const float4 old = first ? *(const float4*)(st + c) : *(const float4*)(x + (size_t)(t - 1) * a.H + c);
-            const float xc[4] = {cur.x, cur.y, cur.z, cur.w}, xo[4] = {old.x, old.y, old.z, old.w};
-            float h[4], o[4];
+    for (int c = threadIdx.x; c < a.H; c += blockDim.x) {
+        const float h = shift_h<DYT>(a, t, c, alpha);
+        const float prev = first ? st[c] : shift_h<DYT>(a, t - 1, c, alpha);
+        sp_st_dt(a.out, a.out_dt, (size_t)t * a.H + c, h + (prev - h) * sp_ld_dt(a.mu, a.mu_dt, c));
+        if (save && last) st[c] = h;
+    }
+}
+
+// Dynamic tanh + shift for widths that are multiples of four: a block takes TS_ROWS neighbouring tokens and a thread
+// four neighbouring columns (16-byte loads of the stream and of the state); a token's h serves as the next token's
+// "previous" without being computed again, so a row costs 1 + 1/TS_ROWS tanh per element instead of two. The state
+// needs no second launch: see the comment at the store.
+#define TS_ROWS 4
+__global__ void dyt_shift_rows_kernel(ShiftArgs a) {
+    const int t0 = blockIdx.x * TS_ROWS;
+    const float alpha = sp_ld_dt(a.alpha, a.w_dt, 0);
+    const float* x = (const float*)a.x;
+    for (int c = threadIdx.x * 4; c < a.H; c += blockDim.x * 4) {
+        float w[4], b[4], mu[4], hp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float w = sp_ld_dt(a.w, a.w_dt, c + i), b = sp_ld_dt(a.b, a.w_dt, c + i);
-                h[i] = tanhf(alpha * xc[i]) * w + b;
-                const float prev = first ? xo[i] : tanhf(alpha * xo[i]) * w + b;
-                o[i] = h[i] + (prev - h[i]) * sp_ld_dt(a.mu, a.mu_dt, c + i);
+        for (int i = 0; i < 4; ++i) {
+            w[i] = sp_ld_dt(a.w, a.w_dt, c + i);
+            b[i] = sp_ld_dt(a.b, a.w_dt, c + i);
+            mu[i] = sp_ld_dt(a.mu, a.mu_dt, c + i);
+        }
+        for (int r = 0; r < TS_ROWS && t0 + r < a.T; ++r) {
+            const int t = t0 + r;
+            const int s = a.token_seq[t];
+            const bool first = t == a.seq_start[s];
+            const int slot = a.seq_slot[s];
+            if (slot < 0 || slot >= a.n_slots) continue;
+            float* st = a.state + (size_t)slot * a.H + c;
+            const float4 cur = *(const float4*)(x + (size_t)t * a.H + c);
+            const float xc[4] = {cur.x, cur.y, cur.z, cur.w};
+            float h[4], prev[4], o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = tanhf(alpha * xc[i]) * w[i] + b[i];
+            if (first) {
+                const float4 p4 = *(const float4*)st;
+                prev[0] = p4.x; prev[1] = p4.y; prev[2] = p4.z; prev[3] = p4.w;
+                // this thread is the only reader of the row in this step, so it is also the one that may overwrite it:
+                // with the h of the sequence's last token of the step
+                const int t_last = a.seq_start[s + 1] - 1;
+                if (t_last == t) {
+                    *(float4*)st = make_float4(h[0], h[1], h[2], h[3]);
+                } else {
+                    const float4 l4 = *(const float4*)(x + (size_t)t_last * a.H + c);
+                    *(float4*)st = make_float4(tanhf(alpha * l4.x) * w[0] + b[0], tanhf(alpha * l4.y) * w[1] + b[1],
+                                               tanhf(alpha * l4.z) * w[2] + b[2], tanhf(alpha * l4.w) * w[3] + b[3]);
+                }
+            } else if (r == 0) {
+                const float4 p4 = *(const float4*)(x + (size_t)(t - 1) * a.H + c);
+                const float xo[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) prev[i] = tanhf(alpha * xo[i]) * w[i] + b[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) prev[i] = hp[i];
             }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { o[i] = h[i] + (prev[i] - h[i]) * mu[i]; hp[i] = h[i]; }
             if (a.out_dt == SP_DT_F32) *(float4*)((float*)a.out + (size_t)t * a.H + c) = make_float4(o[0], o[1], o[2], o[3]);
             else {
                 __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
@@ -97,15 +143,7 @@ __global__ void token_shift_kernel(ShiftArgs a, int save) {
                 pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1;
                 *(uint2*)((__nv_bfloat16*)a.out + (size_t)t * a.H + c) = pk;
             }
-            if (save && last) *(float4*)(st + c) = make_float4(h[0], h[1], h[2], h[3]);
         }
-        return;
-    }
-    for (int c = threadIdx.x; c < a.H; c += blockDim.x) {
-        const float h = shift_h<DYT>(a, t, c, alpha);
-        const float prev = first ? st[c] : shift_h<DYT>(a, t - 1, c, alpha);
-        sp_st_dt(a.out, a.out_dt, (size_t)t * a.H + c, h + (prev - h) * sp_ld_dt(a.mu, a.mu_dt, c));
-        if (save && last) st[c] = h;
     }
 }
 
@@ -130,6 +168,11 @@ SP_API int sp_token_shift(const void* x, int x_dt, const void* w, const void* b,
     if (dyt && x_dt != SP_DT_F32) SP_FAIL("token_shift: the norm reads the 32-bit residual stream");
     ShiftArgs a{x, x_dt, w, b, alpha, w_dt, mu, mu_dt, state, out, out_dt, token_seq, seq_start, seq_slot, T, H, n_slots};
     const int threads = H >= 1024 ? 256 : 128;
+    if (dyt && (H & 3) == 0 && ((((uintptr_t)x) | ((uintptr_t)state) | ((uintptr_t)out)) & 15) == 0) {
+        dyt_shift_rows_kernel<<<(T + TS_ROWS - 1) / TS_ROWS, H >= 2048 ? 256 : 128, 0, stream>>>(a);
+        SP_CHECK_LAUNCH("dyt_shift_rows");
+        return 0;                                      // this kernel stores the state itself
+    }
     if (dyt) token_shift_kernel<true><<<T, threads, 0, stream>>>(a, all_single);
     else token_shift_kernel<false><<<T, threads, 0, stream>>>(a, all_single);
     SP_CHECK_LAUNCH("token_shift");
@@ -386,7 +429,7 @@ diff_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, co
 // The same for steps of few (token, head) pairs over many keys (decoding): eight warps share one pair and take the
 // chunks of 32 visible keys in turn; key and value rows are read in 16- and 8-byte pieces (d a multiple of 8, vd of
 // 4), a lane owns four neighbouring value columns; warp 0 merges the eight parts in warp order.
-#define DD_WARPS 8
+#define DD_WARPS 16
 
 __device__ __forceinline__ void dd_ld8(const float* p, float (&v)[8]) {
     const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
@@ -398,29 +441,51 @@ __device__ __forceinline__ void dd_ld8(const __nv_bfloat16* p, float (&v)[8]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
 }
-__device__ __forceinline__ void dd_ld4(const float* p, float (&v)[4]) {
-    const float4 a = *(const float4*)p;
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-}
-__device__ __forceinline__ void dd_ld4(const __nv_bfloat16* p, float (&v)[4]) {
-    const uint2 raw = *(const uint2*)p;
-    const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+// four neighbouring values as they lie in memory, and their 32-bit values
+struct DdRaw4f { float4 r; };
+struct DdRaw4h { uint2 r; };
+__device__ __forceinline__ void dd_fetch4(const float* p, DdRaw4f& x) { x.r = *(const float4*)p; }
+__device__ __forceinline__ void dd_fetch4(const __nv_bfloat16* p, DdRaw4h& x) { x.r = *(const uint2*)p; }
+__device__ __forceinline__ void dd_open4(const DdRaw4f& x, float (&v)[4]) { v[0] = x.r.x; v[1] = x.r.y; v[2] = x.r.z; v[3] = x.r.w; }
+__device__ __forceinline__ void dd_open4(const DdRaw4h& x, float (&v)[4]) {
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&x.r;
     const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
+template <typename TC> struct DdRaw { using T = DdRaw4f; static constexpr int BATCH = 8; };
+template <> struct DdRaw<__nv_bfloat16> { using T = DdRaw4h; static constexpr int BATCH = 16; };
 
-template <typename TQ, typename TC>
+// Sixteen warps share one (token, head) and take the chunks of 32 visible keys in turn. Per chunk a warp first asks
+// for the value rows (a lane owns four neighbouring columns; in bfloat16 sixteen rows of the chunk are in flight at
+// once), then reads its keys in 16-byte pieces and computes the two scores, so one memory round trip covers both.
+// NV = groups of 128 value columns. Warp 0 merges the parts in warp order.
+__device__ __forceinline__ void dd_cp_async16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dd_cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// ``SR`` key rows of a chunk are staged at a time in the warp's own piece of shared memory by 16-byte asynchronous
+// copies in which neighbouring lanes take neighbouring pieces of a row (a lane that read its own row straight from
+// global memory touched 32 lines per instruction); each lane then reads its key's row from there.
+template <typename TQ, typename TC, int NV>
 __global__ void __launch_bounds__(DD_WARPS * 32)
 diff_decode_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
-                   TQ* __restrict__ out, KvPlace pl, DiffArgs a) {
-    constexpr int NV = DA_MAX_VD / 128;                      // groups of four columns a lane may own
-    __shared__ __align__(16) float qs[2 * DA_MAX_D];
-    __shared__ __align__(16) float part[DD_WARPS][2][DA_MAX_VD];
+                   TQ* __restrict__ out, KvPlace pl, DiffArgs a, int SR) {
+    using Raw = typename DdRaw<TC>::T;
+    constexpr int VB = DdRaw<TC>::BATCH / NV;            // value rows in flight per lane: 16 (bfloat16) or 8, halved for two column groups
+    extern __shared__ __align__(16) float dd_sm[];
+    float* qs = dd_sm;                                   // [2·d]
+    float* part = qs + 2 * a.d;                          // [DD_WARPS][2][vd]
     __shared__ float part_ml[DD_WARPS][4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x / a.H, h = blockIdx.x % a.H;
     const int g = h / (a.H / a.G);
     const int d = a.d, vd = a.vd, kd = 2 * a.d;
+    const int row_pieces = kd * (int)sizeof(TC) / 16;    // 16-byte pieces of a key row
+    const int row_stride = kd * (int)sizeof(TC) + 16;    // bytes; the pad spreads the rows over the banks
+    uint8_t* kbuf = (uint8_t*)(part + (size_t)DD_WARPS * 2 * vd) + (size_t)warp * SR * row_stride;
     const int p = pl.positions[t];
     const int row = sp_checked_row(pl.seq_slot[pl.token_seq[t]], pl.rg);
     const int* pt = pl.page_table + (size_t)row * pl.max_pages;
@@ -441,27 +506,55 @@ diff_decode_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const
     for (int v0 = 32 * warp; v0 < n_vis; v0 += 32 * DD_WARPS) {
         const int vi = v0 + lane;
         const bool valid = vi < n_vis;
-        float s1 = -INFINITY, s2 = -INFINITY;
         int my_page = 0, my_off = 0;
         if (valid) {
             const int j = vi < n_first ? vi : lo + (vi - n_first);
             my_page = sp_checked_page(pt[sp_checked_entry(j / ps, pl.max_pages, pl.rg)], pl.rg);
             my_off = j % ps;
-            const TC* kr = kpool + (((size_t)my_page * a.G + g) * ps + my_off) * kd;
-            float d1 = 0.0f, d2 = 0.0f;
-            for (int c = 0; c < d; c += 8) {
-                float k1[8], k2[8];
-                dd_ld8(kr + c, k1);
-                dd_ld8(kr + d + c, k2);
+        }
+        const size_t my_row = ((size_t)my_page * a.G + g) * ps + my_off;     // lanes beyond the end: row 0 of page 0, weight 0
+        Raw raw[NV][VB];
+        auto fetch = [&](int jj0) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { d1 = fmaf(qs[c + u], k1[u], d1); d2 = fmaf(qs[d + c + u], k2[u], d2); }
+            for (int u = 0; u < VB; ++u) {
+                const size_t r = __shfl_sync(0xffffffffu, my_row, (jj0 + u) & 31);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const int c = 4 * lane + 128 * i;
+                    if (c < vd) dd_fetch4(vpool + r * vd + c, raw[i][u]);
+                }
             }
-            s1 = d1 * a.scale;
-            s2 = d2 * a.scale;
-            if (a.softcap > 0.0f) {
-                s1 = a.softcap * tanhf(s1 / a.softcap);
-                s2 = a.softcap * tanhf(s2 / a.softcap);
+        };
+        fetch(0);
+        float s1 = -INFINITY, s2 = -INFINITY;
+        for (int sub = 0; sub * SR < 32; ++sub) {
+            const int total = SR * row_pieces;
+            for (int e0 = 0; e0 < total; e0 += 32) {
+                const int e = e0 + lane;
+                const int r = min(e / row_pieces, SR - 1), piece = e % row_pieces;
+                const size_t src_row = __shfl_sync(0xffffffffu, my_row, sub * SR + r);
+                if (e < total) dd_cp_async16(kbuf + (size_t)r * row_stride + piece * 16, (const uint8_t*)(kpool + src_row * kd) + piece * 16);
             }
+            dd_cp_async_wait_all();
+            __syncwarp();
+            if (valid && lane / SR == sub) {
+                const TC* kr = (const TC*)(kbuf + (size_t)(lane % SR) * row_stride);
+                float d1 = 0.0f, d2 = 0.0f;
+                for (int c = 0; c < d; c += 8) {
+                    float k1[8], k2[8];
+                    dd_ld8(kr + c, k1);
+                    dd_ld8(kr + d + c, k2);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) { d1 = fmaf(qs[c + u], k1[u], d1); d2 = fmaf(qs[d + c + u], k2[u], d2); }
+                }
+                s1 = d1 * a.scale;
+                s2 = d2 * a.scale;
+                if (a.softcap > 0.0f) {
+                    s1 = a.softcap * tanhf(s1 / a.softcap);
+                    s2 = a.softcap * tanhf(s2 / a.softcap);
+                }
+            }
+            __syncwarp();
         }
         const float n1 = fmaxf(m1, sp_warp_max(s1)), n2 = fmaxf(m2, sp_warp_max(s2));
         const float e1 = valid ? expf(s1 - n1) : 0.0f, e2 = valid ? expf(s2 - n2) : 0.0f;
@@ -472,32 +565,21 @@ diff_decode_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const
         for (int i = 0; i < NV; ++i)
 #pragma unroll
             for (int u = 0; u < 4; ++u) { acc1[i][u] *= c1; acc2[i][u] *= c2; }
-        const int n_valid = min(32, n_vis - v0);
-        for (int jj0 = 0; jj0 < n_valid; jj0 += 8) {
-            float w1[8], w2[8];
-            const TC* vr[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                w1[u] = __shfl_sync(0xffffffffu, e1, (jj0 + u) & 31);      // lanes beyond n_valid hold weight 0
-                w2[u] = __shfl_sync(0xffffffffu, e2, (jj0 + u) & 31);
-                const int pg = __shfl_sync(0xffffffffu, my_page, (jj0 + u) & 31);
-                const int of = __shfl_sync(0xffffffffu, my_off, (jj0 + u) & 31);
-                vr[u] = vpool + (((size_t)pg * a.G + g) * ps + of) * vd;   // page 0, offset 0 for those lanes: readable
-            }
+        for (int jj0 = 0; jj0 < 32; jj0 += VB) {
+            if (jj0 > 0) fetch(jj0);
 #pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                const int c = 4 * lane + 128 * i;
-                if (c < vd) {
-                    float v[8][4];
+            for (int u = 0; u < VB; ++u) {
+                const float w1 = __shfl_sync(0xffffffffu, e1, (jj0 + u) & 31);
+                const float w2 = __shfl_sync(0xffffffffu, e2, (jj0 + u) & 31);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) dd_ld4(vr[u] + c, v[u]);
+                for (int i = 0; i < NV; ++i) {
+                    if (4 * lane + 128 * i < vd) {
+                        float v[4];
+                        dd_open4(raw[i][u], v);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) {
-                            acc1[i][x] = fmaf(w1[u], v[u][x], acc1[i][x]);
-                            acc2[i][x] = fmaf(w2[u], v[u][x], acc2[i][x]);
-                        }
+                        for (int x = 0; x < 4; ++x) { acc1[i][x] = fmaf(w1, v[x], acc1[i][x]); acc2[i][x] = fmaf(w2, v[x], acc2[i][x]); }
+                    }
                 }
             }
         }
@@ -508,8 +590,8 @@ diff_decode_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const
     for (int i = 0; i < NV; ++i) {
         const int c = 4 * lane + 128 * i;
         if (c < vd) {
-            *(float4*)&part[warp][0][c] = make_float4(acc1[i][0], acc1[i][1], acc1[i][2], acc1[i][3]);
-            *(float4*)&part[warp][1][c] = make_float4(acc2[i][0], acc2[i][1], acc2[i][2], acc2[i][3]);
+            *(float4*)&part[((size_t)warp * 2 + 0) * vd + c] = make_float4(acc1[i][0], acc1[i][1], acc1[i][2], acc1[i][3]);
+            *(float4*)&part[((size_t)warp * 2 + 1) * vd + c] = make_float4(acc2[i][0], acc2[i][1], acc2[i][2], acc2[i][3]);
         }
     }
     if (lane == 0) { part_ml[warp][0] = m1; part_ml[warp][1] = l1; part_ml[warp][2] = m2; part_ml[warp][3] = l2; }
@@ -533,8 +615,8 @@ diff_decode_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const
             if (c < vd) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    acc1[i][u] = fmaf(part[w][0][c + u], f1, acc1[i][u]);
-                    acc2[i][u] = fmaf(part[w][1][c + u], f2, acc2[i][u]);
+                    acc1[i][u] = fmaf(part[((size_t)w * 2 + 0) * vd + c + u], f1, acc1[i][u]);
+                    acc2[i][u] = fmaf(part[((size_t)w * 2 + 1) * vd + c + u], f2, acc2[i][u]);
                 }
             }
         }
@@ -579,9 +661,26 @@ SP_API int sp_diff_attention(const void* q, int q_dt, const void* kpool, const v
     if (blocks > 2147483647LL) SP_FAIL("diff_attention: too many (token, head) pairs for one launch");
     const size_t esz = cache_dt == SP_DT_F32 ? 4 : 2;
     if (split && d % 8 == 0 && vd % 4 == 0 && (((uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0 && ((size_t)vd * esz) % 8 == 0) {
+        // shared memory: the query, the warps' parts, and per warp SR staged key rows (as many as fit 200 KB)
+        const size_t dd_fixed = ((size_t)2 * d + (size_t)DD_WARPS * 2 * vd) * sizeof(float);
+        const size_t dd_row = (size_t)2 * d * esz + 16;
+        int SR = 32;
+        while (SR > 1 && dd_fixed + (size_t)DD_WARPS * SR * dd_row > 200 * 1024) SR >>= 1;
+        const size_t dd_smem = dd_fixed + (size_t)DD_WARPS * SR * dd_row;
 #define DD_LAUNCH(TQ, TC)                                                                                             \
-        diff_decode_kernel<TQ, TC><<<(unsigned)blocks, DD_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool,    \
-                                                                                   (const TC*)vpool, (TQ*)out, pl, a)
+        do {                                                                                                          \
+            static SpPerDevice ready;                                                                                 \
+            if (!ready.done()) {                                                                                      \
+                if (cudaFuncSetAttribute(diff_decode_kernel<TQ, TC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess || \
+                    cudaFuncSetAttribute(diff_decode_kernel<TQ, TC, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)   \
+                    SP_FAIL("diff_attention: cannot raise the shared memory limit");                                  \
+                ready.mark();                                                                                         \
+            }                                                                                                         \
+            if (vd <= 128) diff_decode_kernel<TQ, TC, 1><<<(unsigned)blocks, DD_WARPS * 32, dd_smem, stream>>>(       \
+                    (const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, a, SR);                           \
+            else diff_decode_kernel<TQ, TC, 2><<<(unsigned)blocks, DD_WARPS * 32, dd_smem, stream>>>(                 \
+                    (const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, a, SR);                           \
+        } while (0)
         if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) DD_LAUNCH(float, float);
         else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) DD_LAUNCH(__nv_bfloat16, __nv_bfloat16);
         else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) DD_LAUNCH(float, __nv_bfloat16);
@@ -1120,10 +1219,10 @@ __global__ void mingru_chunk_kernel(const float* __restrict__ proj, const void* 
     const float bz = sp_ld_dt(zb, b_dt, c), bx = sp_ld_dt(xb, b_dt, c);
     float2* cell = scratch + (size_t)blockIdx.y * W + c;
     float S = PASS == 1 ? 0.0f : cell->x, A = 1.0f;
-    for (int tb = t0; tb < t0 + n; tb += 4) {
-        float pz[4], px[4], pg[4];
+    for (int tb = t0; tb < t0 + n; tb += 8) {
+        float pz[8], px[8], pg[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {                        // four tokens' loads in flight
+        for (int i = 0; i < 8; ++i) {                        // eight tokens' loads in flight
             const bool in = tb + i < t0 + n;
             const float* row = proj + (size_t)(in ? tb + i : tb) * 3 * W;
             pz[i] = row[c];
@@ -1131,7 +1230,7 @@ __global__ void mingru_chunk_kernel(const float* __restrict__ proj, const void* 
             pg[i] = PASS == 1 ? 0.0f : row[2 * W + c];
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 8; ++i) {
             if (tb + i >= t0 + n) break;
             const float z = sm_sigmoid(pz[i] + bz);
             const float u = px[i] + bx;
@@ -1155,11 +1254,18 @@ __global__ void mingru_chunk_scan_kernel(float2* __restrict__ scratch, float* __
     for (int b = 0; b < s; ++b) chunk += (seq_start[b + 1] - seq_start[b] + MG_CHUNK - 1) / MG_CHUNK;
     const int cnt = seq_start[s + 1] - seq_start[s];
     float S = state[(size_t)slot * W + c];
-    for (int x = 0; x * MG_CHUNK < cnt; ++x, ++chunk) {
-        float2* cell = scratch + (size_t)chunk * W + c;
-        const float2 ab = *cell;
-        cell->x = S;
-        S = fmaf(ab.x, S, ab.y);
+    const int n_chunks = (cnt + MG_CHUNK - 1) / MG_CHUNK;
+    for (int x0 = 0; x0 < n_chunks; x0 += 8) {
+        float2 ab[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (x0 + u < n_chunks) ab[u] = scratch[(size_t)(chunk + x0 + u) * W + c];      // eight cells in flight
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (x0 + u >= n_chunks) break;
+            scratch[(size_t)(chunk + x0 + u) * W + c].x = S;
+            S = fmaf(ab[u].x, S, ab[u].y);
+        }
     }
     state[(size_t)slot * W + c] = S;
 }
