@@ -156,7 +156,7 @@ def cmd_chat(args) -> int:
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="spissa_b200", description="Llama generation on one B200")
+    ap = argparse.ArgumentParser(prog="spissa_b200", description="generation on one B200 for the architectures this library knows")
     sub = ap.add_subparsers(dest="command", required=True)
     g = sub.add_parser("generate", help="generate for one or more prompts given as token ids (or text)")
     g.add_argument("model", nargs="?", help="folder with config.json and model.safetensors")

@@ -85,11 +85,11 @@ __global__ void token_shift_kernel(ShiftArgs a, int save) {
 
 // Dynamic tanh + shift for widths that are multiples of four: a block takes TS_ROWS neighbouring tokens and a thread
 // four neighbouring columns (16-byte loads of the stream and of the state); a token's h serves as the next token's
-// "previous" without being computed again, so a row costs 1 + 1/TS_ROWS tanh per element instead of two. The state
+// "previous" without being computed again, so a row costs 1 + 1/rows tanh per element instead of two. The state
 // needs no second launch: see the comment at the store.
-#define TS_ROWS 4
-__global__ void dyt_shift_rows_kernel(ShiftArgs a) {
-    const int t0 = blockIdx.x * TS_ROWS;
+#define TS_ROWS 4              // for steps of many tokens; a step of few tokens gives every token a block of its own
+__global__ void dyt_shift_rows_kernel(ShiftArgs a, int rows) {
+    const int t0 = blockIdx.x * rows;
     const float alpha = sp_ld_dt(a.alpha, a.w_dt, 0);
     const float* x = (const float*)a.x;
     for (int c = threadIdx.x * 4; c < a.H; c += blockDim.x * 4) {
@@ -100,7 +100,7 @@ __global__ void dyt_shift_rows_kernel(ShiftArgs a) {
             b[i] = sp_ld_dt(a.b, a.w_dt, c + i);
             mu[i] = sp_ld_dt(a.mu, a.mu_dt, c + i);
         }
-        for (int r = 0; r < TS_ROWS && t0 + r < a.T; ++r) {
+        for (int r = 0; r < rows && t0 + r < a.T; ++r) {
             const int t = t0 + r;
             const int s = a.token_seq[t];
             const bool first = t == a.seq_start[s];
@@ -169,7 +169,8 @@ SP_API int sp_token_shift(const void* x, int x_dt, const void* w, const void* b,
     ShiftArgs a{x, x_dt, w, b, alpha, w_dt, mu, mu_dt, state, out, out_dt, token_seq, seq_start, seq_slot, T, H, n_slots};
     const int threads = H >= 1024 ? 256 : 128;
     if (dyt && (H & 3) == 0 && ((((uintptr_t)x) | ((uintptr_t)state) | ((uintptr_t)out)) & 15) == 0) {
-        dyt_shift_rows_kernel<<<(T + TS_ROWS - 1) / TS_ROWS, H >= 2048 ? 256 : 128, 0, stream>>>(a);
+        const int rows = T >= 256 ? TS_ROWS : 1;
+        dyt_shift_rows_kernel<<<(T + rows - 1) / rows, H >= 2048 ? 256 : 128, 0, stream>>>(a, rows);
         SP_CHECK_LAUNCH("dyt_shift_rows");
         return 0;                                      // this kernel stores the state itself
     }

@@ -547,3 +547,24 @@ def test_trace_program_on_a_model_of_this_design(models, tmp_path):
         input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
     compare(traces.collect(steps, str(out), m.vocab), refs_of(m, reqs), 3e-2, "trace program")
+
+
+def test_command_line_generates_from_a_folder_and_from_a_configuration_with_random_weights(models, tmp_path):
+    m = models["c"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "bin", "spissa-b200")
+    prompt = tiny.random_prompt(m.vocab, 12, 4)
+    proc = subprocess.run([sys.executable, exe, "generate", m.folder, "--token-ids", ",".join(map(str, prompt)),
+                           "--max-new-tokens", "5", "--dtype", "fp32", "--ctx", "128"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = json.loads(proc.stdout.strip().splitlines()[0])
+    assert line["tokens"] == D.generate_greedy(m.cfg, m.w, prompt, 5) and line["finish_reason"] == "length"
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(CONFIGS["a"]))
+    proc = subprocess.run([sys.executable, exe, "generate", "--random", str(cfg_file), "--token-ids", "1,2,3",
+                           "--token-ids", "9,8,7,6,5", "--max-new-tokens", "4", "--temp", "0.7", "--seed", "2", "--ctx", "128"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(x) for x in proc.stdout.strip().splitlines()]
+    assert [len(x["tokens"]) for x in lines] == [4, 4]
