@@ -71,8 +71,8 @@ class DuzinexConfig:
                 if heads <= 0 or kvh <= 0 or heads % kvh:
                     raise ConfigError(f"{mw}heads {heads} must be a positive multiple of kv_heads {kvh}")
                 dim = _get(m, "dim", mw)
-                if dim <= 0 or dim % 2:
-                    raise ConfigError(f"{mw}dim {dim} must be positive and even")
+                if dim <= 0:
+                    raise ConfigError(f"{mw}dim {dim} must be positive")
                 mixer = dict(heads=heads, kv_heads=kvh, dim=dim, vdim=_get(m, "vdim", mw),
                              diff=float(_get(m, "diff", mw, _NUM)), scale=float(_get(m, "scale", mw, _NUM)),
                              softcap=_get(m, "softcap", mw, _NUM, optional=True))

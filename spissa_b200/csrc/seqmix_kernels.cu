@@ -229,8 +229,28 @@ __global__ void diff_qkv_store_kernel(const float* __restrict__ qkv, const void*
     const int off = pos % pl.page_size;
     const int row = (nq + nk) * d + G * vd;
     const float* src = qkv + (size_t)t * row;
-    const int dp = d >> 1;                          // pairs per sub-head (d is even)
+    const int dp = d >> 1;                          // pairs per sub-head
     const int kd = (nk / G) * d;                    // a key row of one kv head
+    if (d & 1) {
+        // an odd sub-head size: element by element (two-element stores would not be aligned); the last dim never turns
+        for (int e = threadIdx.x; e < (nq + nk) * d; e += blockDim.x) {
+            const int sh = e / d, i = e - sh * d;
+            float val = src[e] + (bias ? sp_ld_dt(bias, b_dt, e) : 0.0f);
+            if (i < rd) {
+                const int im = i ^ 1;                                     // the other dim of the pair
+                const float other = src[sh * d + im] + (bias ? sp_ld_dt(bias, b_dt, sh * d + im) : 0.0f);
+                const float co = cs[i >> 1], si = cs[half + (i >> 1)];
+                val = (i & 1) ? val * co + other * si : val * co - other * si;
+            }
+            if (sh < nq) {
+                sp_st(q_out, (size_t)t * nq * d + e, val);
+            } else if (place_ok) {
+                const int ck = e - nq * d;
+                const int g = ck / kd, r = ck - g * kd;
+                sp_st(kpool, (((size_t)page * G + g) * pl.page_size + off) * kd + r, val);
+            }
+        }
+    } else
     for (int e = threadIdx.x; e < (nq + nk) * dp; e += blockDim.x) {
         const int sh = e / dp, i = e - sh * dp;
         const int c = sh * d + 2 * i;
@@ -264,7 +284,7 @@ SP_API int sp_diff_qkv_store(const float* qkv, const void* bias, int b_dt, void*
                              const int* page_table, int max_pages, int page_size, const float* inv_freq, int T, int nq,
                              int nk, int G, int d, int vd, int rd, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (d <= 0 || (d & 1) || rd < 0 || rd > d || (rd & 1)) SP_FAIL("qkv_store: sizes d %d, rotated %d must be even, rotated <= d", d, rd);
+    if (d <= 0 || rd < 0 || rd > d || (rd & 1)) SP_FAIL("qkv_store: the rotated dims %d must be even and at most d %d", rd, d);
     if (G <= 0 || nk % G) SP_FAIL("qkv_store: %d key sub-heads are no multiple of %d kv heads", nk, G);
     if (rd > 0 && !inv_freq) SP_FAIL("qkv_store: a frequency table is needed");
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};

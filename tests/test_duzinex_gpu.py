@@ -64,9 +64,12 @@ CONFIGS = {
                          gru(40)], [56, 120, None], loop=None, scale=1.0, eps=1e-3),
     "c": model(48, 150, [gru(48), att(1, 1, 32, 16, window=None, rot=32, base=500.0, cap=2.0, diff=0.5),
                          ret(2, 24, 8, [0.8, 0.999])], [96, 64, 32], loop=(0, 3, 2), scale=7.5),
+    # nothing a multiple of four: the paths without wide loads, an odd map size of which four dims turn
+    "d": model(50, 97, [att(2, 1, 7, 9, window=9, keep=2, rot=4, cap=3.0, diff=0.4), ret(2, 5, 7, [0.7, 0.95]), gru(22)],
+               [30, 26, 34], loop=(0, 2, 2), scale=2.0),
 }
 INIT = {"a": dict(seed=5, std=0.08, norm_std=0.2), "b": dict(seed=9, std=0.06, norm_std=0.1),
-        "c": dict(seed=13, std=0.1, norm_std=0.3)}
+        "c": dict(seed=13, std=0.1, norm_std=0.3), "d": dict(seed=17, std=0.12, norm_std=0.2)}
 
 
 def make(cfg, folder, seed, std, norm_std, patch=None):
@@ -322,7 +325,8 @@ def test_differential_attention_kernels_over_pages(d, vd, H, G, window, keep, ca
 
 
 # ---------------------------------------------------------------------------------------------- whole models
-LENGTHS = {"a": [1, 2, 23, 64, 65, 150], "b": [3, 63, 129, 140, 70, 9], "c": [5, 1, 40, 100, 66, 31]}
+LENGTHS = {"a": [1, 2, 23, 64, 65, 150], "b": [3, 63, 129, 140, 70, 9], "c": [5, 1, 40, 100, 66, 31],
+           "d": [2, 70, 1, 33, 129, 64]}
 
 
 def refs_of(m, reqs):
@@ -342,7 +346,7 @@ def compare(got, ref, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_every_cut_agrees_with_plain(models, name, dtype, tmp_path):
     m = models[name]
     reqs = {f"r{i}": tiny.random_prompt(m.vocab, n, 31 * i + n) for i, n in enumerate(LENGTHS[name])}
