@@ -15,11 +15,17 @@ import torch
 from .engine import Engine
 
 
+MAX_REPLAY_SLOTS = 256       # most requests that a trace keeps alive at a time
+
+
 def replay(model_dir, dtype: str, out_dir, max_tokens: int, lines, done_out, device="cuda:0") -> int:
+    # ``max_tokens`` counts tokens, the cache counts pages: every live request may leave a part of its last page
+    # unused, so there is a page of headroom per slot; a request holds at least one token, so there are never more
+    # live requests than tokens
     page = Engine.PAGE_SIZE
-    n_pages = (max_tokens + page - 1) // page
-    engine = Engine.from_folder(model_dir, dtype=dtype, max_tokens=n_pages * page, max_seqs=max(1, n_pages),
-                                device=device)
+    slots = max(1, min(int(max_tokens), MAX_REPLAY_SLOTS))
+    n_pages = (max_tokens + page - 1) // page + slots
+    engine = Engine.from_folder(model_dir, dtype=dtype, max_tokens=n_pages * page, max_seqs=slots, device=device)
     slots: dict = {}
     for line in lines:
         line = line.strip()

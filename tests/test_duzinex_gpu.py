@@ -572,3 +572,16 @@ def test_command_line_generates_from_a_folder_and_from_a_configuration_with_rand
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [json.loads(x) for x in proc.stdout.strip().splitlines()]
     assert [len(x["tokens"]) for x in lines] == [4, 4]
+
+
+def test_trace_budget_counts_tokens_and_many_short_requests_fit(models, tmp_path):
+    """The trace program's --max-tokens is a count of tokens without padding: a dozen live requests of a few tokens
+    each need a page apiece although together they hold less than two pages' worth."""
+    m = models["d"]
+    reqs = {f"s{i}": tiny.random_prompt(m.vocab, 3 + i, 50 + i) for i in range(12)}
+    steps = traces.ragged_batches(reqs, 12, {rid: 2 for rid in reqs})
+    peak = sum(len(t) for t in reqs.values())
+    assert peak < 2 * 64 * 2
+    out = tmp_path / "out"
+    traces.run_in_process(m.folder, "float32", steps, str(out), max_tokens=peak)
+    compare(traces.collect(steps, str(out), m.vocab), refs_of(m, reqs), 2e-5, "many short requests")
