@@ -846,13 +846,18 @@ def token_shift(x, mu, state, out, step, dyt=None):
         c_void_p(_ptr(step.seq_slot)), T, step.n_seqs, H, int(bool(step.all_single)), c_void_p(_stream())))
 
 
-def diff_qkv_store(qkv, bias, q_out, k_pool, v_pool, meta, inv_freq, nq, nk, G, d, vd, rd):
+def diff_qkv_store(qkv, bias, q_out, k_pool, v_pool, meta, inv_freq, nq, nk, G, d, vd, rd, residual=None, residual_bias=None):
     """Add ``bias``, rotate neighbouring pairs over the first ``rd`` dims of each of the nq + nk sub-heads of size d,
-    store q to ``q_out`` and k (rows of nk/G·d per kv head) and v (rows of vd) into the paged cache."""
+    store q to ``q_out`` and k (rows of nk/G·d per kv head) and v (rows of vd) into the paged cache. With ``residual``
+    (float32 [T, W]) and ``residual_bias`` [W] every token's row of the stream also takes that bias (the output
+    projection's, ahead of the product that accumulates into the stream)."""
     lib = load("seqmix")
     if qkv.dtype != torch.float32:
         raise KernelError("diff_qkv_store reads 32-bit projections")
-    _need_contig(qkv, bias, q_out)
+    _need_contig(qkv, bias, q_out, residual, residual_bias)
+    if residual is not None and (residual.dtype != torch.float32 or residual_bias is None or bias is None
+                                 or residual_bias.dtype != bias.dtype or residual_bias.numel() != residual.shape[1]):
+        raise KernelError("diff_qkv_store adds a bias of the projections' storage type to a float32 stream")
     T = qkv.shape[0]
     pt = meta.page_table
     _declare_bounds("seqmix", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), qkv.device)
@@ -860,7 +865,8 @@ def diff_qkv_store(qkv, bias, q_out, k_pool, v_pool, meta, inv_freq, nq, nk, G, 
         c_void_p(_ptr(qkv)), c_void_p(_ptr(bias)), dt_code(bias) if bias is not None else 0, c_void_p(_ptr(q_out)),
         dt_code(q_out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool), c_void_p(_ptr(meta.token_seq)),
         c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
-        c_void_p(_ptr(inv_freq)), T, nq, nk, G, d, vd, rd, c_void_p(_stream())))
+        c_void_p(_ptr(inv_freq)), T, nq, nk, G, d, vd, rd, c_void_p(_ptr(residual)), c_void_p(_ptr(residual_bias)),
+        residual.shape[1] if residual is not None else 0, c_void_p(_stream())))
 
 
 def diff_attention(q, k_pool, v_pool, out, meta, H, G, d, vd, window, keep_first, scale, softcap, lam, eps, out_scale):

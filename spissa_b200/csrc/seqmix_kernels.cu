@@ -212,10 +212,14 @@ template <typename TO, typename TC>
 __global__ void diff_qkv_store_kernel(const float* __restrict__ qkv, const void* __restrict__ bias, int b_dt,
                                       TO* __restrict__ q_out, TC* __restrict__ kpool, TC* __restrict__ vpool, KvPlace pl,
                                       const float* __restrict__ inv_freq, int T, int nq, int nk, int G, int d, int vd,
-                                      int rd) {
+                                      int rd, float* __restrict__ stream, const void* __restrict__ stream_bias, int width) {
     extern __shared__ float cs[];                  // [2][rd/2]
     const int t = blockIdx.x;
     if (t >= T) return;
+    // the output projection's bias goes into the token's row of the residual stream here, ahead of the product that
+    // accumulates into it: one launch less than adding it behind
+    if (stream)
+        for (int c = threadIdx.x; c < width; c += blockDim.x) stream[(size_t)t * width + c] += sp_ld_dt(stream_bias, b_dt, c);
     const int pos = pl.positions[t];
     const int half = rd >> 1;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -282,16 +286,18 @@ __global__ void diff_qkv_store_kernel(const float* __restrict__ qkv, const void*
 SP_API int sp_diff_qkv_store(const float* qkv, const void* bias, int b_dt, void* q_out, int q_dt, void* kpool, void* vpool,
                              int cache_dt, const int* token_seq, const int* positions, const int* seq_slot,
                              const int* page_table, int max_pages, int page_size, const float* inv_freq, int T, int nq,
-                             int nk, int G, int d, int vd, int rd, cudaStream_t stream) {
+                             int nk, int G, int d, int vd, int rd, float* residual, const void* residual_bias, int width,
+                             cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || rd < 0 || rd > d || (rd & 1)) SP_FAIL("qkv_store: the rotated dims %d must be even and at most d %d", rd, d);
     if (G <= 0 || nk % G) SP_FAIL("qkv_store: %d key sub-heads are no multiple of %d kv heads", nk, G);
     if (rd > 0 && !inv_freq) SP_FAIL("qkv_store: a frequency table is needed");
+    if (residual && !bias) SP_FAIL("qkv_store: the stream's bias comes with the projections' biases (one storage type)");
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
     const size_t smem = (size_t)rd * sizeof(float);
 #define QS_LAUNCH(TO, TC)                                                                                          \
     diff_qkv_store_kernel<TO, TC><<<T, 128, smem, stream>>>(qkv, bias, b_dt, (TO*)q_out, (TC*)kpool, (TC*)vpool, pl, \
-                                                           inv_freq, T, nq, nk, G, d, vd, rd)
+                                                           inv_freq, T, nq, nk, G, d, vd, rd, residual, residual_bias, width)
     if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) QS_LAUNCH(float, float);
     else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) QS_LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) QS_LAUNCH(float, __nv_bfloat16);

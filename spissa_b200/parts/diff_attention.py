@@ -92,7 +92,9 @@ class DiffAttention(Mixer):
             qkv = self.qkv(x, out_dtype=torch.float32)             # bias and rotation read unrounded products
         with phase("rotary+kv_append_ms"):
             q = torch.empty(T, nh * 2 * d, dtype=self.rt.act_dtype, device=x.device)
-            K.diff_qkv_store(qkv, self.qkv_bias, q, cache.k_pool, cache.v_pool, cache, inv_freq, 2 * nh, 2 * g, g, d, vd, rd)
+            # the output bias enters the stream here, ahead of the output projection that accumulates into it
+            K.diff_qkv_store(qkv, self.qkv_bias, q, cache.k_pool, cache.v_pool, cache, inv_freq, 2 * nh, 2 * g, g, d, vd, rd,
+                             residual if self.o_bias is not None else None, self.o_bias)
         with phase("attention_ms"):
             ctx = torch.empty(T, nh * vd, dtype=self.rt.act_dtype, device=x.device)
             args = (nh, g, d, vd, self.window, self.keep_first, self.scale, self.softcap, self.lam, self.eps, 1.0 - self.diff)
@@ -105,5 +107,3 @@ class DiffAttention(Mixer):
                 K.diff_attention(q, cache.k_pool, cache.v_pool, ctx, cache, *args)
         with phase("o_projection+attention_residual_ms"):
             self.o(ctx, out=residual, accumulate=True)
-            if self.o_bias is not None:
-                K.add_bias(residual, self.o_bias)

@@ -143,6 +143,11 @@ def test_dynamic_tanh_and_polynorm_kernels(out_dtype):
     zz = z.double()
     ref = 0.7 * D.unit_rms(zz, 1e-4) - 1.3 * D.unit_rms(zz ** 2, 1e-4) + 0.45 * D.unit_rms(zz ** 3, 1e-4) + 0.2
     assert worst(act, ref) <= (5e-6 if out_dtype == torch.float32 else 5e-3)
+    # a bias on the rows of a 32-bit matrix
+    rows32 = x.clone().to(DEV)
+    bias = torch.randn(200, generator=g).to(out_dtype)
+    K.add_bias(rows32, bias.to(DEV))
+    assert worst(rows32, x.double() + bias.double()) <= 1e-6
 
 
 def test_token_shift_kernel_carries_the_last_row_in_the_state():
@@ -178,7 +183,8 @@ def test_token_shift_kernel_carries_the_last_row_in_the_state():
     assert worst(o[0], (a[6] + (a[5] - a[6]) * mu)) <= 1e-6 and torch.equal(state[2].cpu(), a[21])
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(3, 8, 16), (1, 40, 24), (2, 16, 70), (2, 128, 130), (1, 72, 256), (1, 130, 8)])
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 8, 16), (1, 40, 24), (2, 16, 70), (2, 128, 130), (1, 72, 256), (1, 130, 8),
+                                             (2, 100, 40), (2, 32, 32)])
 def test_retention_kernel(heads, dim, vdim):
     """Sequences of 50 and 39 tokens run in chunks (where the key size allows), the single token and the portions
     below token by token; a chunk boundary lies inside nothing here, the next test crosses several."""
@@ -264,7 +270,7 @@ def test_mingru_kernel_both_branches_of_the_candidate():
 
 
 @pytest.mark.parametrize("d,vd,H,G", [(16, 16, 2, 2), (32, 64, 4, 1), (64, 128, 2, 1), (128, 32, 1, 1), (128, 128, 2, 2), (24, 40, 2, 1),
-                                      (12, 20, 3, 3), (16, 20, 16, 4)])
+                                      (12, 20, 3, 3), (16, 20, 16, 4), (64, 64, 2, 1), (32, 32, 4, 2), (16, 128, 1, 1)])
 @pytest.mark.parametrize("window,keep,cap", [(0, 0, 0.0), (50, 0, 4.0), (70, 66, 0.0), (130, 3, 2.0)])
 def test_differential_attention_kernels_over_pages(d, vd, H, G, window, keep, cap):
     """The prompt kernel on the tensor cores (where its sizes are built) and the kernels for any sizes (one warp per
