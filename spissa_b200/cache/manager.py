@@ -123,16 +123,20 @@ class CacheManager:
         self.cache_group: dict = {}
         by_need: dict = {}
         self.bundles: dict = {}                          # cache id -> names of the caches a run asked for together
-        for cid, req in requests.items():
+
+        def ask(cid, req):
             if req is None:
-                continue
+                return
             if isinstance(req, CacheBundle):
-                # each named request becomes a cache of its own under the id (cid, name)
-                self.bundles[cid] = [name for name, _ in req.parts]
+                # each named request becomes a cache of its own under the id (cid, name); a bundle inside a bundle likewise
+                self.bundles[cid] = [name for name, r in req.parts if r is not None]
                 for name, r in req.parts:
-                    by_need.setdefault(r, []).append((cid, name))
-                continue
+                    ask((cid, name), r)
+                return
             by_need.setdefault(req, []).append(cid)
+
+        for cid, req in requests.items():
+            ask(cid, req)
         for req, cids in by_need.items():
             if isinstance(req, KVCacheRequest):
                 name = f"kv{len(self.kv_groups)}" + (f"_w{req.window}" if req.window else "") + \

@@ -69,12 +69,16 @@ class ModelSpec:
     head: PartSpec
     max_position: int
     extras: dict = field(default_factory=dict)
+    streams: int = 1          # copies of the residual stream side by side in a token's row (hyper-connections): the
+    #                           embedding's output fills them all, the layers' blocks mix them, the final norm reads their sum
 
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
         if not self.schedule:
             raise ValueError("a model needs a non-empty layer schedule")
+        if self.streams < 1 or (self.streams > 1 and any(e.adds_embedding for e in self.schedule)):
+            raise ValueError("several residual streams and layers that take the embedding in again do not go together")
         writers = {}
         for pos, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.layers)):

@@ -55,6 +55,7 @@ MODULES = {
     "host_step": "host_step.cu",
     "seqmix": "seqmix_kernels.cu",
     "diff_flash": "diff_flash.cu",
+    "hybrid": "hybrid_kernels.cu",
 }
 
 

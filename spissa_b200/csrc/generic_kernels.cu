@@ -610,7 +610,7 @@ __device__ __forceinline__ float ag_dot(const float* __restrict__ qv, const __nv
 template <typename TQ, typename TC, bool SPLIT>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
-                         TQ* __restrict__ out, KvPlace pl, int T, int nh, int nkv, int hd, int window,
+                         TQ* __restrict__ out, KvPlace pl, int T, int nh, int nkv, int hd, int vd, int window,
                          float scale) {
     __shared__ __align__(16) float qs[AG_WARPS][AG_MAX_HD];
     __shared__ float part_ml[AG_WARPS][2];
@@ -660,12 +660,12 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
                 pj[u] = __shfl_sync(0xffffffffu, e, jj0 + u);
                 const int pg = __shfl_sync(0xffffffffu, my_page, jj0 + u);
                 const int of = __shfl_sync(0xffffffffu, my_off, jj0 + u);
-                vr[u] = vpool + (((size_t)pg * nkv + g) * ps + of) * hd;
+                vr[u] = vpool + (((size_t)pg * nkv + g) * ps + of) * vd;
             }
 #pragma unroll
             for (int i = 0; i < AG_MAX_HD / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) {
+                if (d < vd) {
                     float v[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) v[u] = jj0 + u < n_valid ? sp_ld(vr[u], d) : 0.0f;
@@ -682,7 +682,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 #pragma unroll
         for (int i = 0; i < AG_MAX_HD / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < hd) qs[warp][d] = acc[i];
+            if (d < vd) qs[warp][d] = acc[i];
         }
         if (lane == 0) { part_ml[warp][0] = m; part_ml[warp][1] = l; }
         __syncthreads();
@@ -699,7 +699,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 #pragma unroll
             for (int i = 0; i < AG_MAX_HD / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(qs[w][d], f, acc[i]);
+                if (d < vd) acc[i] = fmaf(qs[w][d], f, acc[i]);
             }
         }
         l = ll;
@@ -707,16 +707,17 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) sp_st(out, (size_t)t * nh * hd + (size_t)h * hd + d, acc[i] / l);
+        if (d < vd) sp_st(out, (size_t)t * nh * vd + (size_t)h * vd + d, acc[i] / l);
     }
 }
 
 SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, const void* vpool, int cache_dt,
                                 void* out, const int* token_seq, const int* positions, const int* seq_slot,
                                 const int* page_table, int max_pages, int page_size, int T, int nh, int nkv,
-                                int hd, int window, float scale, cudaStream_t stream) {
+                                int hd, int vd, int window, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > AG_MAX_HD) SP_FAIL("attention: head_dim %d is beyond this kernel's limit %d", hd, AG_MAX_HD);
+    if (vd <= 0 || vd > AG_MAX_HD) SP_FAIL("attention: value size %d is beyond this kernel's limit %d", vd, AG_MAX_HD);
     if (nkv <= 0 || nh % nkv) SP_FAIL("attention: %d heads are no multiple of %d kv heads", nh, nkv);
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
     const long long warps = (long long)T * nh;
@@ -727,9 +728,9 @@ SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, cons
 #define AG_LAUNCH(TQ, TC)                                                                                              \
     do {                                                                                                               \
         if (split)                                                                                                     \
-            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, window, scale); \
+            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale); \
         else                                                                                                           \
-            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, window, scale); \
+            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, vd, window, scale); \
     } while (0)
     if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) AG_LAUNCH(float, float);
     else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) AG_LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -1,0 +1,863 @@
+// Parts of layers that mix several kinds of sublayers, with the small kernels that surround them.
+//
+//   streams_norm      several copies of the residual stream (hyper-connections): the streams take a sublayer's
+//                     output in (X_t ← Σ_s mix[s,t] X_s + out_t y), and the next sublayer's input is the layer norm
+//                     (mean and variance, a weight, no bias) of Σ_s in_s X_s; with one stream and no coefficients it
+//                     is a plain layer norm
+//   streams_expand    the embedding's rows copied into every stream
+//   conv_qk_store     a short causal convolution over time on every channel of q, k, v (its last inputs are a
+//                     sequence's state), rotation of dim i with dim i + dims/2 over the first dims of every head,
+//                     a weightless rms norm of q and k per head, q out, k / v to pages
+//   gla               gated linear attention: S_t = diag(α_t) S_{t-1} + k_t v_tᵀ, o_t = S_tᵀ q_t with a decay per key
+//                     channel from a low-rank projection, rms norm with a weight per head, gate silu(g)
+//   gelu_tanh, clamped_glu     activations of feed-forwards
+//   moe_select        sigmoid router: choice among the best groups of experts with a correction, weights without it
+//   moe_plan / moe_up / moe_down / moe_combine      the chosen experts' products over token lists sorted by expert
+//
+// Everything but the experts' products is computed in 32-bit (FFMA, expf / tanhf / sqrtf / division without
+// fast-math); stores round to the activation type. States are 32-bit. Every output row is reduced in an order that
+// depends on its own sequence only, never on the batch or on how the tokens were cut into steps.
+#include "common.cuh"
+
+SP_API const char* sp_hybrid_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(hybrid)
+
+__device__ __forceinline__ float hy_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float hy_silu(float x) { return x / (1.0f + expf(-x)); }
+
+// ============================================================== streams: update, mix and layer norm
+#define HC_MAX_STREAMS 8
+struct HcArgs {
+    float* x;                 // [T][S·W] the streams of every token, updated in place when ``y`` is given
+    float* y;                 // [T][W] a sublayer's output, or null; left zeroed for the next sublayer to add into
+    const float* mix;         // [S][S] (from, to), or null: every stream keeps itself
+    const float* outc;        // [S] how much of y each stream takes, or null: all of it
+    const float* inc;         // [S] coefficients of the norm's input, or null: the sum of the streams
+    const void* w; int w_dt;  // the norm's weight [W], or null: no norm, the update only
+    void* out; int out_dt;    // [n_rows][W]
+    const int* rows;          // optional gather of token rows (without ``y`` only)
+    int n_rows, S, W;
+    float eps;
+};
+
+__global__ void streams_norm_kernel(HcArgs a) {
+    extern __shared__ float u[];                       // [W] the norm's input
+    __shared__ float red[32];
+    __shared__ float cm[HC_MAX_STREAMS * HC_MAX_STREAMS], co[HC_MAX_STREAMS], ci[HC_MAX_STREAMS];
+    const int r = blockIdx.x;
+    if (r >= a.n_rows) return;
+    const int S = a.S, W = a.W;
+    if (threadIdx.x < S * S) cm[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.0f : 0.0f);
+    if (threadIdx.x < S) {
+        co[threadIdx.x] = a.outc ? a.outc[threadIdx.x] : 1.0f;
+        ci[threadIdx.x] = a.inc ? a.inc[threadIdx.x] : 1.0f;
+    }
+    __syncthreads();
+    const size_t row = a.rows ? (size_t)a.rows[r] : (size_t)r;
+    float* xr = a.x + row * S * W;
+    float part = 0.0f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float xs[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * W + c] : 0.0f;
+        if (a.y) {
+            const float yv = a.y[row * W + c];
+            a.y[row * W + c] = 0.0f;
+            float nx[HC_MAX_STREAMS];
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+                if (t >= S) break;
+                float v = 0.0f;
+#pragma unroll
+                for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                    if (s < S) v = fmaf(cm[s * S + t], xs[s], v);
+                nx[t] = fmaf(co[t], yv, v);
+            }
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                if (t < S) { xs[t] = nx[t]; xr[(size_t)t * W + c] = nx[t]; }
+        }
+        if (a.w) {
+            float v = 0.0f;
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                if (s < S) v = fmaf(ci[s], xs[s], v);
+            u[c] = v;
+            part += v;
+        }
+    }
+    if (!a.w) return;
+    const float mean = sp_block_sum(part, red) / (float)W;
+    float dev = 0.0f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float dlt = u[c] - mean;
+        dev = fmaf(dlt, dlt, dev);
+    }
+    const float var = sp_block_sum(dev, red) / (float)W;
+    const float inv = 1.0f / sqrtf(var + a.eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x)
+        sp_st_dt(a.out, a.out_dt, (size_t)r * W + c, (u[c] - mean) * inv * sp_ld_dt(a.w, a.w_dt, c));
+}
+
+static SpPerDevice streams_norm_ready;
+
+SP_API int sp_streams_norm(float* x, float* y, const float* mix, const float* outc, const float* inc, const void* w,
+                           int w_dt, void* out, int out_dt, const int* rows, int n_rows, int S, int W, float eps,
+                           cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (S < 1 || S > HC_MAX_STREAMS) SP_FAIL("streams_norm: %d streams, this kernel takes 1 to %d", S, HC_MAX_STREAMS);
+    if (y && rows) SP_FAIL("streams_norm: an update runs over all rows");
+    const size_t smem = (size_t)W * sizeof(float);
+    if (smem > 200 * 1024) SP_FAIL("streams_norm: a row of %d does not fit shared memory", W);
+    if (smem > 48 * 1024 && !streams_norm_ready.done()) {
+        if (cudaFuncSetAttribute(streams_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            SP_FAIL("streams_norm: cannot raise the shared memory limit");
+        streams_norm_ready.mark();
+    }
+    HcArgs a{x, y, mix, outc, inc, w, w_dt, out, out_dt, rows, n_rows, S, W, eps};
+    streams_norm_kernel<<<n_rows, W >= 1024 ? 256 : 128, smem, stream>>>(a);
+    SP_CHECK_LAUNCH("streams_norm");
+    return 0;
+}
+
+__global__ void streams_expand_kernel(const float* __restrict__ h, float* __restrict__ x, size_t T, int S, int W) {
+    const size_t n = T * (size_t)S * W;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / ((size_t)S * W);
+        x[e] = h[t * W + e % W];
+    }
+}
+
+SP_API int sp_streams_expand(const float* h, float* x, int T, int S, int W, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t n = (size_t)T * S * W;
+    const size_t want = (n + 255) / 256;
+    streams_expand_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(h, x, (size_t)T, S, W);
+    SP_CHECK_LAUNCH("streams_expand");
+    return 0;
+}
+
+// ============================================================== short convolution, rotation, unit rms, cache write
+// qkv row (32-bit) = [q: nh·d | k: nkv·d | v: nkv·vd] = C channels. The convolution of channel c at a token reads the
+// channel's projected values of the token and of the taps−1 tokens before it: from this step's rows where the step
+// has them, from state[slot][r][c] (r = 0 the oldest) where they came with earlier steps, zeros before the sequence's
+// start (a fresh slot's state is zero). One block per token, a warp per head; the head's values pass through shared
+// memory so that a lane reaches both halves of a rotated pair.
+#define CQ_MAX_DIM 256
+#define CQ_WARPS 4
+#define CQ_MAX_TAPS 8
+struct CqArgs {
+    const float* qkv; int ld;
+    const void* conv; int conv_dt; int taps;      // [C][taps]; taps 1 and conv null: no convolution
+    float* state; int n_slots;                     // [slots][taps−1][C]
+    const float* inv_freq; int rd;                 // rd 0: no rotation
+    void* q_out; int q_dt;
+    void* kpool; void* vpool; int cache_dt;
+    const int* token_seq; const int* positions; const int* seq_row; const int* page_table; int max_pages, page_size;
+    const int* seq_start; const int* seq_slot;
+    int T, nh, nkv, d, vd;
+    float eps, v_scale;
+    int unit_rms;                                  // 1: q and k leave with unit rms per head
+    int save_inline;                               // 1: every sequence brings one token, so the token's block also shifts the state
+    SpRange rg;
+};
+
+__device__ __forceinline__ float cq_conv(const CqArgs& a, int t, int local, int slot, int c, int C) {
+    const float cur = a.qkv[(size_t)t * a.ld + c];
+    if (a.taps <= 1) return a.conv ? cur * sp_ld_dt(a.conv, a.conv_dt, c) : cur;
+    float u[CQ_MAX_TAPS];
+    const int n = a.taps - 1;
+    float* st = a.state + (size_t)slot * n * C + c;
+#pragma unroll
+    for (int j = 0; j < CQ_MAX_TAPS; ++j) {
+        if (j >= a.taps) break;
+        const int l = local - n + j;               // place of tap j among the step's tokens of this sequence
+        u[j] = l >= 0 ? a.qkv[(size_t)(t - n + j) * a.ld + c] : st[(size_t)(n + l) * C];
+    }
+    float y = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CQ_MAX_TAPS; ++j) {
+        if (j >= a.taps) break;
+        y = fmaf(sp_ld_dt(a.conv, a.conv_dt, (size_t)c * a.taps + j), u[j], y);
+    }
+    if (a.save_inline) {
+        // local is 0 here, so u[j] is the state's row j for j < n, and the token's own value last
+#pragma unroll
+        for (int r = 0; r < CQ_MAX_TAPS - 1; ++r)
+            if (r < n) st[(size_t)r * C] = u[r + 1];
+    }
+    return y;
+}
+
+__global__ void __launch_bounds__(CQ_WARPS * 32) conv_qk_store_kernel(CqArgs a) {
+    __shared__ float hv[CQ_WARPS][CQ_MAX_DIM];
+    __shared__ float cs[2][CQ_MAX_DIM / 2];
+    const int t = blockIdx.x;
+    if (t >= a.T) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = a.token_seq[t];
+    const int pos = a.positions[t];
+    const int local = t - a.seq_start[s];
+    const int slot = a.seq_slot[s];
+    if (a.taps > 1 && (slot < 0 || slot >= a.n_slots)) return;
+    const int half = a.rd >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * a.inv_freq[i];
+        cs[0][i] = cosf(ang);
+        cs[1][i] = sinf(ang);
+    }
+    __syncthreads();
+    const int d = a.d, vd = a.vd, nh = a.nh, nkv = a.nkv;
+    const int C = (nh + nkv) * d + nkv * vd;
+    bool place = true;
+    int page = 0;
+    {
+        const int row = a.seq_row[s];
+        if (!sp_index_ok(row, a.rg.n_rows, a.rg, 402) || !sp_index_ok(pos / a.page_size, a.max_pages, a.rg, 403)) place = false;
+        else {
+            page = a.page_table[(size_t)row * a.max_pages + pos / a.page_size];
+            place = sp_index_ok(page, a.rg.n_pages, a.rg, 401);
+        }
+    }
+    const int off = pos % a.page_size;
+    for (int hh = warp; hh < nh + 2 * nkv; hh += CQ_WARPS) {
+        const bool is_v = hh >= nh + nkv;
+        const int size = is_v ? vd : d;
+        const int cb = is_v ? (nh + nkv) * d + (hh - nh - nkv) * vd : hh * d;
+        __syncwarp();
+        for (int i = lane; i < size; i += 32) hv[warp][i] = cq_conv(a, t, local, slot, cb + i, C);
+        __syncwarp();
+        if (is_v) {
+            if (place) {
+                const size_t vb = (((size_t)page * nkv + (hh - nh - nkv)) * a.page_size + off) * vd;
+                for (int i = lane; i < vd; i += 32) sp_st_dt(a.vpool, a.cache_dt, vb + i, hv[warp][i] * a.v_scale);
+            }
+            continue;
+        }
+        for (int i = lane; i < half; i += 32) {
+            const float x0 = hv[warp][i], x1 = hv[warp][i + half];
+            hv[warp][i] = x0 * cs[0][i] - x1 * cs[1][i];
+            hv[warp][i + half] = x1 * cs[0][i] + x0 * cs[1][i];
+        }
+        __syncwarp();
+        float inv = 1.0f;
+        if (a.unit_rms) {
+            float ss = 0.0f;
+            for (int i = lane; i < d; i += 32) ss = fmaf(hv[warp][i], hv[warp][i], ss);
+            ss = sp_warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+        }
+        if (hh < nh) {
+            for (int i = lane; i < d; i += 32) sp_st_dt(a.q_out, a.q_dt, (size_t)t * nh * d + (size_t)hh * d + i, hv[warp][i] * inv);
+        } else if (place) {
+            const size_t kb = (((size_t)page * nkv + (hh - nh)) * a.page_size + off) * d;
+            for (int i = lane; i < d; i += 32) sp_st_dt(a.kpool, a.cache_dt, kb + i, hv[warp][i] * inv);
+        }
+    }
+}
+
+// the state after a step of several tokens per sequence: the last taps−1 projected values of each sequence, the
+// older ones moved down where the step brought fewer (rows ascending: a row only reads rows above itself)
+__global__ void conv_state_save_kernel(CqArgs a, int B, int C) {
+    const int s = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (s >= B || c >= C) return;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int t0 = a.seq_start[s], cnt = a.seq_start[s + 1] - t0, n = a.taps - 1;
+    float* st = a.state + (size_t)slot * n * C + c;
+    for (int r = 0; r < n; ++r) {
+        const int l = cnt - n + r;
+        st[(size_t)r * C] = l >= 0 ? a.qkv[(size_t)(t0 + l) * a.ld + c] : st[(size_t)(r + cnt) * C];
+    }
+}
+
+SP_API int sp_conv_qk_store(const float* qkv, int ld, const void* conv, int conv_dt, int taps, float* state, int n_slots,
+                            const float* inv_freq, int rd, void* q_out, int q_dt, void* kpool, void* vpool, int cache_dt,
+                            const int* token_seq, const int* positions, const int* seq_row, const int* page_table,
+                            int max_pages, int page_size, const int* seq_start, const int* seq_slot, int T, int B, int nh,
+                            int nkv, int d, int vd, float eps, float v_scale, int unit_rms, int all_single,
+                            cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || d > CQ_MAX_DIM || vd <= 0 || vd > CQ_MAX_DIM) SP_FAIL("conv_qk_store: head sizes %d / %d are beyond %d", d, vd, CQ_MAX_DIM);
+    if (taps < 1 || taps > CQ_MAX_TAPS) SP_FAIL("conv_qk_store: %d taps, this kernel takes 1 to %d", taps, CQ_MAX_TAPS);
+    if (taps > 1 && (!conv || !state)) SP_FAIL("conv_qk_store: a convolution needs its weights and a state");
+    if (rd < 0 || (rd & 1) || rd > d) SP_FAIL("conv_qk_store: %d rotated dims do not fit a head of %d", rd, d);
+    CqArgs a{qkv, ld, conv, conv_dt, taps, state, n_slots, inv_freq, rd, q_out, q_dt, kpool, vpool, cache_dt,
+             token_seq, positions, seq_row, page_table, max_pages, page_size, seq_start, seq_slot, T, nh, nkv, d, vd,
+             eps, v_scale, unit_rms, (all_single && taps > 1) ? 1 : 0, sp_range_host};
+    conv_qk_store_kernel<<<T, CQ_WARPS * 32, 0, stream>>>(a);
+    SP_CHECK_LAUNCH("conv_qk_store");
+    if (taps > 1 && !all_single) {
+        const int C = (nh + nkv) * d + nkv * vd;
+        conv_state_save_kernel<<<dim3(B, (C + 127) / 128), 128, 0, stream>>>(a, B, C);
+        SP_CHECK_LAUNCH("conv_state_save");
+    }
+    return 0;
+}
+
+// ============================================================== gated linear attention
+// proj row (32-bit) = [q: H·d | k: H·d | v: H·vd | g: H·vd | r: rank]. The decay of key channel e of head h at a
+// token is α = sigmoid(z)^(1/τ) = exp(logsigmoid(z) / τ) with z = a2[h·d+e, :] · r + b[h·d+e].
+struct GlaArgs {
+    const float* proj; int ld;
+    float* state; int n_slots;           // [slots][H][d][vd]
+    const void* a2; const void* a2b; const void* nw; int w_dt;    // [H·d][rank], [H·d], norm weight [vd]
+    float* o_raw;                        // [T][H·vd] (the step kernel's raw outputs)
+    void* out; int out_dt;               // [T][H·vd]
+    const int* seq_start; const int* seq_slot;
+    int B, H, d, vd, rank;
+    float inv_tau, eps, out_scale;
+};
+
+__device__ __forceinline__ float gla_alpha(float z, float inv_tau) {
+    const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));       // log sigmoid(z)
+    return expf(ls * inv_tau);
+}
+
+// Token by token. One CTA per (sequence, head): the state S [d][vd] lives in shared memory for the whole step; thread
+// (j, y) owns column j of the rows i ≡ y (mod DY); the DY partial sums of a column are added in the order of y.
+__global__ void gla_scan_kernel(GlaArgs a, int vdr, int DY) {
+    extern __shared__ float sm[];
+    const int d = a.d, vd = a.vd, rank = a.rank;
+    float* S = sm;                                   // [d][vd]
+    float* qs = S + (size_t)d * vd;                  // q/√d [d]
+    float* ks = qs + d;                              // k [d]
+    float* al = ks + d;                              // α [d]
+    float* rr = al + d;                              // r [rank]
+    float* red = rr + rank;                          // [DY][vdr]
+    float* o = red + (size_t)DY * vdr;               // [vdr]
+    float* A2 = o + vdr;                             // [d][rank]
+    __shared__ float inv_rms;
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int j = threadIdx.x % vdr, y = threadIdx.x / vdr;
+    float* gS = a.state + ((size_t)slot * a.H + h) * d * vd;
+    for (int e = threadIdx.x; e < d * vd; e += blockDim.x) S[e] = gS[e];
+    for (int e = threadIdx.x; e < d * rank; e += blockDim.x) A2[e] = sp_ld_dt(a.a2, a.w_dt, (size_t)h * d * rank + e);
+    const float qscale = 1.0f / sqrtf((float)d);
+    const int Hd = a.H * d, Hv = a.H * vd;
+    for (int t = a.seq_start[s]; t < a.seq_start[s + 1]; ++t) {
+        const float* row = a.proj + (size_t)t * a.ld;
+        __syncthreads();
+        for (int e = threadIdx.x; e < rank; e += blockDim.x) rr[e] = row[2 * Hd + 2 * Hv + e];
+        __syncthreads();
+        for (int e = threadIdx.x; e < d; e += blockDim.x) {
+            qs[e] = row[h * d + e] * qscale;
+            ks[e] = row[Hd + h * d + e];
+            float z = sp_ld_dt(a.a2b, a.w_dt, h * d + e);
+            for (int r = 0; r < rank; ++r) z = fmaf(A2[e * rank + r], rr[r], z);
+            al[e] = gla_alpha(z, a.inv_tau);
+        }
+        __syncthreads();
+        float part = 0.0f;
+        if (j < vd) {
+            const float v = row[2 * Hd + h * vd + j];
+            for (int i = y; i < d; i += DY) {
+                const float sv = fmaf(al[i], S[i * vd + j], ks[i] * v);
+                S[i * vd + j] = sv;
+                part = fmaf(sv, qs[i], part);
+            }
+        }
+        red[y * vdr + j] = part;
+        __syncthreads();
+        if (y == 0) {
+            float sum = 0.0f;
+            for (int yy = 0; yy < DY; ++yy) sum += red[yy * vdr + j];
+            o[j] = j < vd ? sum : 0.0f;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float ss = 0.0f;
+            for (int c = threadIdx.x; c < vd; c += 32) ss = fmaf(o[c], o[c], ss);
+            ss = sp_warp_sum(ss);
+            if (threadIdx.x == 0) inv_rms = 1.0f / sqrtf(ss / (float)vd + a.eps);
+        }
+        __syncthreads();
+        if (y == 0 && j < vd)
+            sp_st_dt(a.out, a.out_dt, (size_t)t * Hv + h * vd + j,
+                     o[j] * inv_rms * sp_ld_dt(a.nw, a.w_dt, j) * hy_silu(row[2 * Hd + Hv + h * vd + j]) * a.out_scale);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < d * vd; e += blockDim.x) gS[e] = S[e];
+}
+
+// rms norm with the weight, the gate, the scale, the store; grid (T, H)
+__global__ void gla_finish_kernel(GlaArgs a) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int vd = a.vd, Hv = a.H * vd;
+    const float* o = a.o_raw + (size_t)t * Hv + h * vd;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < vd; c += blockDim.x) ss = fmaf(o[c], o[c], ss);
+    ss = sp_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)vd + a.eps);
+    const float* g = a.proj + (size_t)t * a.ld + 2 * a.H * a.d + Hv + h * vd;
+    for (int c = threadIdx.x; c < vd; c += blockDim.x)
+        sp_st_dt(a.out, a.out_dt, (size_t)t * Hv + h * vd + c, o[c] * inv * sp_ld_dt(a.nw, a.w_dt, c) * hy_silu(g[c]) * a.out_scale);
+}
+
+// A decode step (one token per sequence): the state is streamed once, straight from and to global memory; grid
+// (sequences, heads, blocks of 32 value columns), thread (x, y) takes column x of the rows i ≡ y (mod 8); the eight
+// partial sums of a column are added in the order of y.
+__global__ void __launch_bounds__(256) gla_step_kernel(GlaArgs a) {
+    extern __shared__ float sm[];
+    const int d = a.d, vd = a.vd, rank = a.rank;
+    float* qs = sm;
+    float* ks = qs + d;
+    float* al = ks + d;
+    float* rr = al + d;                    // [rank]
+    float* red = rr + rank;                // [8][32]
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int t = a.seq_start[s];
+    const int Hd = a.H * d, Hv = a.H * vd;
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    const int j = blockIdx.z * 32 + x;
+    const float* row = a.proj + (size_t)t * a.ld;
+    const float qscale = 1.0f / sqrtf((float)d);
+    for (int e = threadIdx.x; e < rank; e += blockDim.x) rr[e] = row[2 * Hd + 2 * Hv + e];
+    __syncthreads();
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+        qs[e] = row[h * d + e] * qscale;
+        ks[e] = row[Hd + h * d + e];
+        float z = sp_ld_dt(a.a2b, a.w_dt, h * d + e);
+        for (int r = 0; r < rank; ++r) z = fmaf(sp_ld_dt(a.a2, a.w_dt, ((size_t)h * d + e) * rank + r), rr[r], z);
+        al[e] = gla_alpha(z, a.inv_tau);
+    }
+    __syncthreads();
+    float part = 0.0f;
+    if (j < vd) {
+        const float v = row[2 * Hd + h * vd + j];
+        float* gS = a.state + ((size_t)slot * a.H + h) * d * vd + j;
+        for (int i0 = y; i0 < d; i0 += 32) {
+            float st[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) st[u] = i0 + 8 * u < d ? gS[(size_t)(i0 + 8 * u) * vd] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + 8 * u;
+                if (i >= d) break;
+                const float sv = fmaf(al[i], st[u], ks[i] * v);
+                gS[(size_t)i * vd] = sv;
+                part = fmaf(sv, qs[i], part);
+            }
+        }
+    }
+    red[y * 32 + x] = part;
+    __syncthreads();
+    if (y == 0 && j < vd) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int yy = 0; yy < 8; ++yy) sum += red[yy * 32 + x];
+        a.o_raw[(size_t)t * Hv + h * vd + j] = sum;
+    }
+}
+
+static SpPerDevice gla_ready;
+
+// mode 0: token by token (any portion); 1: a decode step (needs o_raw)
+SP_API int sp_gla(const float* proj, int ld, float* state, int n_slots, const void* a2, const void* a2b, const void* nw,
+                  int w_dt, float* o_raw, void* out, int out_dt, const int* seq_start, const int* seq_slot, int B, int H,
+                  int d, int vd, int rank, float tau, float eps, float out_scale, int mode, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (d <= 0 || vd <= 0 || vd > 1024 || rank <= 0 || rank > 1024) SP_FAIL("gla: sizes d %d, vd %d, rank %d are outside this kernel's range", d, vd, rank);
+    if (!(tau > 0.0f)) SP_FAIL("gla: tau must be positive");
+    GlaArgs a{proj, ld, state, n_slots, a2, a2b, nw, w_dt, o_raw, out, out_dt, seq_start, seq_slot, B, H, d, vd, rank,
+              1.0f / tau, eps, out_scale};
+    if (!gla_ready.done()) {
+        if (cudaFuncSetAttribute(gla_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess)
+            SP_FAIL("gla: cannot raise the shared memory limit");
+        gla_ready.mark();
+    }
+    if (mode == 1) {
+        if (!o_raw) SP_FAIL("gla: a decode step needs room for its raw outputs");
+        const size_t smem = ((size_t)3 * d + rank + 256) * sizeof(float);
+        if (smem > 48 * 1024) SP_FAIL("gla (step): key size %d is beyond this kernel's range", d);
+        gla_step_kernel<<<dim3(B, H, (vd + 31) / 32), 256, smem, stream>>>(a);
+        SP_CHECK_LAUNCH("gla_step");
+        gla_finish_kernel<<<dim3(B, H), 128, 0, stream>>>(a);
+        SP_CHECK_LAUNCH("gla_finish");
+        return 0;
+    }
+    const int vdr = (vd + 31) / 32 * 32;
+    int DY = 256 / vdr;
+    if (DY < 1) DY = 1;
+    if (DY > d) DY = d;
+    const size_t smem = ((size_t)d * vd + 3 * d + rank + (size_t)DY * vdr + vdr + (size_t)d * rank) * sizeof(float);
+    if (smem > 220 * 1024) SP_FAIL("gla: a state of %d x %d does not fit shared memory", d, vd);
+    gla_scan_kernel<<<dim3(B, H), vdr * DY, smem, stream>>>(a, vdr, DY);
+    SP_CHECK_LAUNCH("gla");
+    return 0;
+}
+
+// ============================================================== activations of feed-forwards
+__global__ void gelu_tanh_kernel(const void* __restrict__ z, int z_dt, void* __restrict__ out, int out_dt, size_t n) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const float v = sp_ld_dt(z, z_dt, e);
+        sp_st_dt(out, out_dt, e, 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))));
+    }
+}
+
+SP_API int sp_gelu_tanh(const void* z, int z_dt, void* out, int out_dt, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const long long want = (n + 255) / 256;
+    gelu_tanh_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(z, z_dt, out, out_dt, (size_t)n);
+    SP_CHECK_LAUNCH("gelu_tanh");
+    return 0;
+}
+
+// g = min(gate, limit), u = clamp(up, ±limit), out = g · sigmoid(slope · g) · (u + 1)
+__device__ __forceinline__ float hy_clamped_glu(float g, float u, float limit, float slope) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * hy_sigmoid(slope * g) * (u + 1.0f);
+}
+
+// gu row = [gate (F) | up (F)]
+__global__ void clamped_glu_kernel(const void* __restrict__ gu, int gu_dt, void* __restrict__ out, int out_dt, size_t rows,
+                                   int F, float limit, float slope) {
+    const size_t n = rows * (size_t)F;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / F;
+        const int c = (int)(e % F);
+        sp_st_dt(out, out_dt, e, hy_clamped_glu(sp_ld_dt(gu, gu_dt, r * 2 * F + c), sp_ld_dt(gu, gu_dt, r * 2 * F + F + c), limit, slope));
+    }
+}
+
+SP_API int sp_clamped_glu(const void* gu, int gu_dt, void* out, int out_dt, int rows, int F, float limit, float slope,
+                          cudaStream_t stream) {
+    if (rows <= 0 || F <= 0) return 0;
+    const size_t n = (size_t)rows * F;
+    const size_t want = (n + 255) / 256;
+    clamped_glu_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(gu, gu_dt, out, out_dt, (size_t)rows, F, limit, slope);
+    SP_CHECK_LAUNCH("clamped_glu");
+    return 0;
+}
+
+// ============================================================== the router's choice
+// z [T][E] (32-bit logits). s = sigmoid(z); choice c = s + correction. The experts form ``n_groups`` equal groups of
+// neighbours; a group's score is the sum of its two largest c; only experts of the ``keep`` best groups can be chosen
+// (n_groups ≤ 1: all). The ``top`` largest allowed c are chosen (among equals the lowest index); their weights are
+// their s divided by the sum of those s (+ 1e-20). One warp per token; lane l holds experts l, l+32, ...
+#define MS_MAX_E 512
+#define MS_WARPS 4
+__device__ __forceinline__ void ms_take(float& bv, int& bi, float ov, int oi) {
+    if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+}
+
+__global__ void __launch_bounds__(MS_WARPS * 32)
+moe_select_kernel(const float* __restrict__ z, const void* __restrict__ corr, int corr_dt, int* __restrict__ ids,
+                  float* __restrict__ wts, int T, int E, int top, int n_groups, int keep) {
+    __shared__ float ch[MS_WARPS][MS_MAX_E];        // choice scores; −inf once chosen or not allowed
+    __shared__ float sc[MS_WARPS][MS_MAX_E];
+    __shared__ float gs[MS_WARPS][MS_MAX_E];        // group scores
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * MS_WARPS + warp;
+    if (t >= T) return;
+    for (int e = lane; e < E; e += 32) {
+        const float s = hy_sigmoid(z[(size_t)t * E + e]);
+        sc[warp][e] = s;
+        ch[warp][e] = s + (corr ? sp_ld_dt(corr, corr_dt, e) : 0.0f);
+    }
+    __syncwarp();
+    if (n_groups > 1) {
+        const int gsz = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float b1 = -INFINITY, b2 = -INFINITY;
+            for (int e = g * gsz; e < (g + 1) * gsz; ++e) {
+                const float c = ch[warp][e];
+                if (c > b1) { b2 = b1; b1 = c; }
+                else if (c > b2) b2 = c;
+            }
+            gs[warp][g] = gsz > 1 ? b1 + b2 : b1;
+        }
+        __syncwarp();
+        // the ``keep`` best groups stay; the others' experts leave the choice
+        for (int r = 0; r < n_groups - keep; ++r) {
+            // drop the worst group still in (among equals the highest index, so that the lowest index wins a place)
+            float wv = 0.0f;
+            int wi = -1;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gs[warp][g];
+                if (v == INFINITY) continue;                        // already dropped
+                if (wi < 0 || v < wv || (v == wv && g > wi)) { wv = v; wi = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+                if (oi >= 0 && (wi < 0 || ov < wv || (ov == wv && oi > wi))) { wv = ov; wi = oi; }
+            }
+            if (wi < 0) break;
+            for (int e = wi * gsz + lane; e < (wi + 1) * gsz; e += 32) ch[warp][e] = -INFINITY;
+            if (lane == 0) gs[warp][wi] = INFINITY;
+            __syncwarp();
+        }
+    }
+    float sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float bv = 0.0f;
+        int bi = -1;
+        for (int e = lane; e < E; e += 32) {
+            const float c = ch[warp][e];
+            if (c != -INFINITY) ms_take(bv, bi, c, e);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ms_take(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (bi < 0) bi = 0;                                         // fewer allowed experts than ``top``: refused on the host
+        const float s = sc[warp][bi];
+        sum += s;
+        if (lane == 0) {
+            ids[(size_t)t * top + k] = bi;
+            wts[(size_t)t * top + k] = s;
+            ch[warp][bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    __syncwarp();
+    const float den = sum + 1e-20f;
+    for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] = wts[(size_t)t * top + k] / den;
+}
+
+SP_API int sp_moe_select(const float* z, const void* corr, int corr_dt, int* ids, float* wts, int T, int E, int top,
+                         int n_groups, int keep, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > MS_MAX_E) SP_FAIL("moe_select: %d experts, this kernel takes up to %d", E, MS_MAX_E);
+    if (n_groups < 1) n_groups = 1;
+    if (E % n_groups) SP_FAIL("moe_select: %d experts do not form %d equal groups", E, n_groups);
+    if (n_groups > 1 && (keep < 1 || keep > n_groups)) SP_FAIL("moe_select: %d of %d groups cannot be kept", keep, n_groups);
+    const int allowed = n_groups > 1 ? keep * (E / n_groups) : E;
+    if (top < 1 || top > allowed) SP_FAIL("moe_select: %d experts cannot be chosen among %d allowed", top, allowed);
+    moe_select_kernel<<<(T + MS_WARPS - 1) / MS_WARPS, MS_WARPS * 32, 0, stream>>>(z, corr, corr_dt, ids, wts, T, E, top, n_groups, keep);
+    SP_CHECK_LAUNCH("moe_select");
+    return 0;
+}
+
+// ============================================================== the chosen experts' products
+// A pair p = token · top + k names one chosen expert of one token. ``moe_plan`` sorts the pairs by expert (pairs of
+// one expert in ascending order) and cuts every expert's list into tiles of ME_TM rows: (expert, first place in the
+// sorted list, rows); unused entries of the tile table (it is sized for the worst case) say expert −1.
+#define ME_TM 32
+__global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int* __restrict__ counts) {
+    __shared__ int red[32];
+    const int e = blockIdx.x;
+    int c = 0;
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) c += ids[p] == e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int sum = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) sum += red[w];
+        counts[e] = sum;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict__ counts, int E, int* __restrict__ sorted,
+                 int* __restrict__ tiles /* [max_tiles][3] */, int max_tiles) {
+    __shared__ int start, tile0, mine, wsum[8], running;
+    const int e = blockIdx.x;
+    if (threadIdx.x == 0) {
+        int s = 0, t0 = 0;
+        for (int x = 0; x < e; ++x) { s += counts[x]; t0 += (counts[x] + ME_TM - 1) / ME_TM; }
+        start = s; tile0 = t0; mine = counts[e]; running = 0;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < n_pairs; base += 256) {
+        const int p = base + threadIdx.x;
+        const bool hit = p < n_pairs && ids[p] == e;
+        const unsigned b = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) wsum[warp] = __popc(b);
+        __syncthreads();
+        int before = running;
+        for (int w = 0; w < warp; ++w) before += wsum[w];
+        if (hit) sorted[start + before + __popc(b & ((1u << lane) - 1u))] = p;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < 8; ++w) tot += wsum[w];
+            running += tot;
+        }
+        __syncthreads();
+    }
+    const int n_mine = (mine + ME_TM - 1) / ME_TM;
+    for (int i = threadIdx.x; i < n_mine; i += blockDim.x) {
+        if (tile0 + i >= max_tiles) break;
+        tiles[(tile0 + i) * 3 + 0] = e;
+        tiles[(tile0 + i) * 3 + 1] = start + i * ME_TM;
+        tiles[(tile0 + i) * 3 + 2] = min(ME_TM, mine - i * ME_TM);
+    }
+    if (e == E - 1)
+        for (int i = tile0 + n_mine + threadIdx.x; i < max_tiles; i += blockDim.x) tiles[i * 3] = -1;
+}
+
+SP_API int sp_moe_tile_rows() { return ME_TM; }
+
+SP_API int sp_moe_plan(const int* ids, int n_pairs, int E, int* counts, int* sorted, int* tiles, int max_tiles,
+                       cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    moe_count_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts);
+    SP_CHECK_LAUNCH("moe_count");
+    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles);
+    SP_CHECK_LAUNCH("moe_place");
+    return 0;
+}
+
+// FFMA tiles: ME_TM rows x ME_BN columns, K in blocks of ME_BK; thread (ty, tx) owns rows 2ty, 2ty+1 and columns
+// 4tx … 4tx+3. Every output adds its products in the order of k, whatever tile it falls into.
+#define ME_BN 64
+#define ME_BK 32
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+moe_up_kernel(const TA* __restrict__ x, const TW* __restrict__ wgu, const int* __restrict__ sorted,
+              const int* __restrict__ tiles, TA* __restrict__ act, int top, int W, int F, float limit, float slope) {
+    __shared__ float As[ME_BK][ME_TM + 1];
+    __shared__ __align__(16) float Bg[ME_BK][ME_BN], Bu[ME_BK][ME_BN];
+    __shared__ int tok[ME_TM];
+    const int e = tiles[blockIdx.x * 3];
+    if (e < 0) return;
+    const int first = tiles[blockIdx.x * 3 + 1], rows = tiles[blockIdx.x * 3 + 2];
+    const int n0 = blockIdx.y * ME_BN;
+    if (threadIdx.x < ME_TM) tok[threadIdx.x] = threadIdx.x < rows ? sorted[first + threadIdx.x] / top : -1;
+    __syncthreads();
+    const TW* wg = wgu + (size_t)e * 2 * F * W;
+    const TW* wu = wg + (size_t)F * W;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float ag[2][4] = {}, au[2][4] = {};
+    for (int k0 = 0; k0 < W; k0 += ME_BK) {
+        {
+            const int m = threadIdx.x >> 3, kk = (threadIdx.x & 7) * 4;
+            const int t = tok[m];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                As[kk + u][m] = (t >= 0 && k0 + kk + u < W) ? sp_ld(x, (size_t)t * W + k0 + kk + u) : 0.0f;
+            const int n = threadIdx.x >> 2, k8 = (threadIdx.x & 3) * 8;
+            const bool in = n0 + n < F;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool ok = in && k0 + k8 + u < W;
+                Bg[k8 + u][n] = ok ? sp_ld(wg, (size_t)(n0 + n) * W + k0 + k8 + u) : 0.0f;
+                Bu[k8 + u][n] = ok ? sp_ld(wu, (size_t)(n0 + n) * W + k0 + k8 + u) : 0.0f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < ME_BK; ++k) {
+            const float a0 = As[k][2 * ty], a1 = As[k][2 * ty + 1];
+            const float4 g4 = *(const float4*)&Bg[k][4 * tx];
+            const float4 u4 = *(const float4*)&Bu[k][4 * tx];
+            const float g[4] = {g4.x, g4.y, g4.z, g4.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                ag[0][c] = fmaf(a0, g[c], ag[0][c]); ag[1][c] = fmaf(a1, g[c], ag[1][c]);
+                au[0][c] = fmaf(a0, uu[c], au[0][c]); au[1][c] = fmaf(a1, uu[c], au[1][c]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int m = 2 * ty + r;
+        if (m >= rows) continue;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int n = n0 + 4 * tx + c;
+            if (n < F) sp_st(act, (size_t)(first + m) * F + n, hy_clamped_glu(ag[r][c], au[r][c], limit, slope));
+        }
+    }
+}
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const TA* __restrict__ act, const TW* __restrict__ wd, const int* __restrict__ sorted,
+                const int* __restrict__ tiles, const float* __restrict__ wts, float* __restrict__ out, int W, int F) {
+    __shared__ float As[ME_BK][ME_TM + 1];
+    __shared__ __align__(16) float Bs[ME_BK][ME_BN];
+    const int e = tiles[blockIdx.x * 3];
+    if (e < 0) return;
+    const int first = tiles[blockIdx.x * 3 + 1], rows = tiles[blockIdx.x * 3 + 2];
+    const int n0 = blockIdx.y * ME_BN;
+    const TW* w = wd + (size_t)e * W * F;
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[2][4] = {};
+    for (int k0 = 0; k0 < F; k0 += ME_BK) {
+        {
+            const int m = threadIdx.x >> 3, kk = (threadIdx.x & 7) * 4;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                As[kk + u][m] = (m < rows && k0 + kk + u < F) ? sp_ld(act, (size_t)(first + m) * F + k0 + kk + u) : 0.0f;
+            const int n = threadIdx.x >> 2, k8 = (threadIdx.x & 3) * 8;
+            const bool in = n0 + n < W;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                Bs[k8 + u][n] = (in && k0 + k8 + u < F) ? sp_ld(w, (size_t)(n0 + n) * F + k0 + k8 + u) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < ME_BK; ++k) {
+            const float a0 = As[k][2 * ty], a1 = As[k][2 * ty + 1];
+            const float4 b4 = *(const float4*)&Bs[k][4 * tx];
+            const float b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                acc[0][c] = fmaf(a0, b[c], acc[0][c]);
+                acc[1][c] = fmaf(a1, b[c], acc[1][c]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int m = 2 * ty + r;
+        if (m >= rows) continue;
+        const int p = sorted[first + m];
+        const float wt = wts[p];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int n = n0 + 4 * tx + c;
+            if (n < W) out[(size_t)p * W + n] = acc[r][c] * wt;
+        }
+    }
+}
+
+// y[t] += Σ_k out[t·top + k] in the order of k
+__global__ void moe_combine_kernel(const float* __restrict__ out, float* __restrict__ y, size_t T, int top, int W) {
+    const size_t n = T * (size_t)W;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / W;
+        const int c = (int)(e % W);
+        float v = 0.0f;
+        for (int k = 0; k < top; ++k) v += out[(t * top + k) * W + c];
+        y[e] += v;
+    }
+}
+
+SP_API int sp_moe_experts(const void* x, int x_dt, const void* wgu, const void* wd, int w_dt, const int* sorted,
+                          const int* tiles, int max_tiles, const float* wts, void* act, float* out_pairs, float* y,
+                          int T, int top, int W, int F, float limit, float slope, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const dim3 g_up(max_tiles, (F + ME_BN - 1) / ME_BN), g_down(max_tiles, (W + ME_BN - 1) / ME_BN);
+#define ME_LAUNCH(TA, TW)                                                                                             \
+    do {                                                                                                              \
+        moe_up_kernel<TA, TW><<<g_up, 256, 0, stream>>>((const TA*)x, (const TW*)wgu, sorted, tiles, (TA*)act, top, W, F, limit, slope); \
+        SP_CHECK_LAUNCH("moe_up");                                                                                    \
+        moe_down_kernel<TA, TW><<<g_down, 256, 0, stream>>>((const TA*)act, (const TW*)wd, sorted, tiles, wts, out_pairs, W, F); \
+        SP_CHECK_LAUNCH("moe_down");                                                                                  \
+    } while (0)
+    if (x_dt == SP_DT_F32 && w_dt == SP_DT_F32) ME_LAUNCH(float, float);
+    else if (x_dt == SP_DT_BF16 && w_dt == SP_DT_BF16) ME_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (x_dt == SP_DT_F32 && w_dt == SP_DT_BF16) ME_LAUNCH(float, __nv_bfloat16);
+    else SP_FAIL("moe_experts: unsupported dtype codes %d/%d", x_dt, w_dt);
+#undef ME_LAUNCH
+    const size_t n = (size_t)T * W;
+    const size_t want = (n + 255) / 256;
+    moe_combine_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(out_pairs, y, (size_t)T, top, W);
+    SP_CHECK_LAUNCH("moe_combine");
+    return 0;
+}

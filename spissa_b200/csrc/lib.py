@@ -174,8 +174,9 @@ def rope_kv_write(qkv, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd, rd, w
         c_void_p(_ptr(inv_freq)), T, nh, nkv, hd, rd, int(bool(write_kv)), c_void_p(_stream())))
 
 
-def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
-    """Causal attention of every token of the step over its sequence's cached keys."""
+def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale, vd=None):
+    """Causal attention of every token of the step over its sequence's cached keys; ``vd``: the size of a value row
+    when it differs from a key row's (``out`` is then [T, nh·vd])."""
     lib = load("generic")
     T = q.shape[0]
     _need_contig(q, out)
@@ -185,7 +186,7 @@ def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
         c_void_p(_ptr(q)), dt_code(q), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool),
         c_void_p(_ptr(out)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)),
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
-        T, nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_stream())))
+        T, nh, nkv, hd, int(vd or hd), int(window or 0), c_float(scale), c_void_p(_stream())))
 
 
 def silu_mul(gu, out):
@@ -995,3 +996,145 @@ def diff_flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tile
         c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
         n_seqs, n_q_tiles, H, G, d, vd, int(window or 0), int(keep_first or 0), c_float(scale), c_float(softcap or 0.0),
         c_float(lam), c_float(eps), c_float(out_scale), c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ hybrid: several streams, a convolved windowed
+# attention, gated linear attention, routed experts
+def streams_norm(x, S, W, out=None, weight=None, eps=0.0, y=None, mix=None, out_coef=None, in_coef=None, rows=None):
+    """The streams ``x`` (float32 [T, S·W]) take a sublayer's output ``y`` (float32 [T, W], left zeroed) in:
+    X_t ← Σ_s mix[s,t] X_s + out_coef[t]·y (``mix`` None: every stream keeps itself, ``out_coef`` None: ones); then
+    ``out`` [rows, W] = layer norm (mean and variance, ``weight``, no bias) of Σ_s in_coef[s] X_s (``in_coef`` None:
+    the plain sum). Either half may be left out (``y`` None / ``weight`` None). ``rows`` gathers (without ``y``)."""
+    lib = load("hybrid")
+    if x.dtype != torch.float32 or (y is not None and y.dtype != torch.float32):
+        raise KernelError("streams_norm works on the 32-bit residual streams")
+    for c in (mix, out_coef, in_coef):
+        if c is not None and c.dtype != torch.float32:
+            raise KernelError("streams_norm takes its coefficients as float32")
+    _need_contig(x, y, mix, out_coef, in_coef, weight, out, rows)
+    n_rows = out.shape[0] if out is not None else x.shape[0]
+    _check("hybrid", lib.sp_streams_norm(
+        c_void_p(_ptr(x)), c_void_p(_ptr(y)), c_void_p(_ptr(mix)), c_void_p(_ptr(out_coef)), c_void_p(_ptr(in_coef)),
+        c_void_p(_ptr(weight)), dt_code(weight) if weight is not None else 0, c_void_p(_ptr(out)),
+        dt_code(out) if out is not None else 0, c_void_p(_ptr(rows)), n_rows, int(S), int(W), c_float(eps),
+        c_void_p(_stream())))
+
+
+def streams_expand(h, x, S):
+    """x [T, S·W] (float32): every stream a copy of ``h`` [T, W]."""
+    lib = load("hybrid")
+    _need_contig(h, x)
+    T, W = h.shape
+    _check("hybrid", lib.sp_streams_expand(c_void_p(_ptr(h)), c_void_p(_ptr(x)), T, int(S), W, c_void_p(_stream())))
+
+
+def conv_qk_store(qkv, conv, taps, state, q_out, k_pool, v_pool, meta, step, inv_freq, nh, nkv, d, vd, rd, eps,
+                  v_scale=1.0, unit_rms=True):
+    """``qkv`` rows [q | k | v] (float32): a causal convolution of ``taps`` taps over time on every channel (``conv``
+    [C, taps]; ``state`` float32 [slots, taps−1, C] holds each sequence's last inputs), rotation of dim i with dim
+    i + rd/2 over the first ``rd`` dims of each q and k head, unit rms per head, q to ``q_out``, k and v (times
+    ``v_scale``) into the paged cache."""
+    lib = load("hybrid")
+    if qkv.dtype != torch.float32 or (state is not None and state.dtype != torch.float32):
+        raise KernelError("conv_qk_store reads 32-bit projections and keeps a 32-bit state")
+    _need_contig(qkv, conv, state, q_out)
+    T = qkv.shape[0]
+    pt = meta.page_table
+    _declare_bounds("hybrid", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), qkv.device)
+    global launches
+    if taps > 1 and not step.all_single:
+        launches += 1                                  # the state is stored by a second launch behind the first
+    _check("hybrid", lib.sp_conv_qk_store(
+        c_void_p(_ptr(qkv)), qkv.shape[1], c_void_p(_ptr(conv)), dt_code(conv) if conv is not None else 0, int(taps),
+        c_void_p(_ptr(state)), state.shape[0] if state is not None else 0, c_void_p(_ptr(inv_freq)), int(rd),
+        c_void_p(_ptr(q_out)), dt_code(q_out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool),
+        c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)),
+        pt.shape[1], meta.page_size, c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), T, step.n_seqs,
+        nh, nkv, d, vd, c_float(eps), c_float(v_scale), int(bool(unit_rms)), int(bool(step.all_single)),
+        c_void_p(_stream())))
+
+
+def gla(proj, state, a2, a2_bias, norm_weight, out, step, H, d, vd, rank, tau, eps, out_scale=1.0):
+    """Gated linear attention. proj rows [q | k | v | g | r] (float32, r the low-rank input of the decays); state
+    float32 [slots, H, d, vd]; out [T, H·vd] = rms norm (``norm_weight`` [vd]) of the heads' outputs ⊙ silu(g) ·
+    ``out_scale``."""
+    lib = load("hybrid")
+    if proj.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("gla runs on 32-bit projections and state")
+    _need_contig(proj, state, a2, a2_bias, norm_weight, out)
+    o_raw, mode = None, 0
+    global launches
+    if step.all_single and d <= 2048:
+        launches += 1                                  # the states streamed once, then the norm and the gate
+        o_raw = torch.empty(proj.shape[0] * H * vd, dtype=torch.float32, device=proj.device)
+        mode = 1
+    _check("hybrid", lib.sp_gla(
+        c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(a2)),
+        c_void_p(_ptr(a2_bias)), c_void_p(_ptr(norm_weight)), _w_dt(a2, a2_bias, norm_weight), c_void_p(_ptr(o_raw)),
+        c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), step.n_seqs,
+        H, d, vd, rank, c_float(tau), c_float(eps), c_float(out_scale), mode, c_void_p(_stream())))
+
+
+def gelu_tanh(z, out):
+    """out = ½ z (1 + tanh(√(2/π) (z + 0.044715 z³))), element by element."""
+    lib = load("hybrid")
+    _need_contig(z, out)
+    _check("hybrid", lib.sp_gelu_tanh(c_void_p(_ptr(z)), dt_code(z), c_void_p(_ptr(out)), dt_code(out),
+                                      c_longlong(z.numel()), c_void_p(_stream())))
+
+
+def clamped_glu(gu, out, limit, slope=1.702):
+    """gu rows [gate | up]: g = min(gate, limit), u = clamp(up, ±limit), out = g · sigmoid(slope · g) · (u + 1)."""
+    lib = load("hybrid")
+    rows, F = out.shape
+    _need_contig(gu, out)
+    if gu.shape[1] != 2 * F:
+        raise KernelError("clamped_glu wants gu [rows, 2·F] and out [rows, F]")
+    _check("hybrid", lib.sp_clamped_glu(c_void_p(_ptr(gu)), dt_code(gu), c_void_p(_ptr(out)), dt_code(out), rows, F,
+                                        c_float(limit), c_float(slope), c_void_p(_stream())))
+
+
+def moe_select(z, correction, ids, weights, top, n_groups=1, keep=1):
+    """From router logits ``z`` (float32 [T, E]): the ``top`` experts per token by sigmoid(z) + correction among the
+    ``keep`` best of ``n_groups`` groups (a group's score: its two largest), and their weights sigmoid(z) / Σ."""
+    lib = load("hybrid")
+    if z.dtype != torch.float32 or ids.dtype != torch.int32 or weights.dtype != torch.float32:
+        raise KernelError("moe_select takes float32 logits and writes int32 ids and float32 weights")
+    _need_contig(z, correction, ids, weights)
+    T, E = z.shape
+    _check("hybrid", lib.sp_moe_select(
+        c_void_p(_ptr(z)), c_void_p(_ptr(correction)), dt_code(correction) if correction is not None else 0,
+        c_void_p(_ptr(ids)), c_void_p(_ptr(weights)), T, E, int(top), int(n_groups or 1), int(keep or 1),
+        c_void_p(_stream())))
+
+
+def moe_tile_rows() -> int:
+    return int(load("hybrid").sp_moe_tile_rows())
+
+
+def moe_experts(x, ids, weights, w_gate_up, w_down, y, top, limit, slope=1.702):
+    """y (float32 [T, W]) += Σ_k weights[t,k] · expert_{ids[t,k]}(x[t]) with clamped-GLU experts: ``w_gate_up``
+    [E, 2F, W] (gate rows, then up rows), ``w_down`` [E, W, F]. The (token, expert) pairs are sorted by expert on the
+    device; nothing comes back to the host."""
+    lib = load("hybrid")
+    _need_contig(x, ids, weights, w_gate_up, w_down, y)
+    T, W = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    n_pairs = T * top
+    tm = moe_tile_rows()
+    max_tiles = (n_pairs + tm - 1) // tm + E
+    dev = x.device
+    book = torch.empty(E + n_pairs + 3 * max_tiles, dtype=torch.int32, device=dev)
+    counts, order, tiles = book[:E], book[E:E + n_pairs], book[E + n_pairs:]
+    act = torch.empty(n_pairs, F, dtype=x.dtype, device=dev)
+    out_pairs = torch.empty(n_pairs, W, dtype=torch.float32, device=dev)
+    global launches
+    launches += 4
+    _check("hybrid", lib.sp_moe_plan(c_void_p(_ptr(ids)), n_pairs, E, c_void_p(_ptr(counts)), c_void_p(_ptr(order)),
+                                     c_void_p(_ptr(tiles)), max_tiles, c_void_p(_stream())))
+    _check("hybrid", lib.sp_moe_experts(
+        c_void_p(_ptr(x)), dt_code(x), c_void_p(_ptr(w_gate_up)), c_void_p(_ptr(w_down)), _w_dt(w_gate_up, w_down),
+        c_void_p(_ptr(order)), c_void_p(_ptr(tiles)), max_tiles, c_void_p(_ptr(weights)), c_void_p(_ptr(act)),
+        c_void_p(_ptr(out_pairs)), c_void_p(_ptr(y)), T, int(top), W, F, c_float(limit), c_float(slope),
+        c_void_p(_stream())))

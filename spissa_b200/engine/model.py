@@ -119,6 +119,10 @@ class Model:
         else:
             with phase("embedding_ms"):
                 h = self.embedding.forward(step)
+        if self.spec.streams > 1 and h is not None:
+            streams = torch.empty(h.shape[0], self.spec.streams * h.shape[1], dtype=torch.float32, device=h.device)
+            K.streams_expand(h, streams, self.spec.streams)        # every stream starts as the embedding's output
+            h = streams
         h0 = None
         if any(e.adds_embedding for e in self.spec.schedule):
             h0 = h.clone()                                 # what the embedding left, for the runs that take it in again

@@ -2,7 +2,8 @@
 from .base import (Block, CacheBundle, FeedForward, KVCacheRequest, Mixer, Norm, Part, PositionEncoding, Runtime,
                    StateRequest, WeightSpec)
 from .registry import build_part, known_parts, register_part, unregister_part
-from . import norm, rope, attention, diff_attention, recurrent, mlp, block, embedding  # noqa: F401  (registration)
+from . import (norm, rope, attention, conv_attention, diff_attention, recurrent, parallel, mlp, block,  # noqa: F401
+               embedding)                                                                     # (registration)
 
 __all__ = ["Block", "CacheBundle", "FeedForward", "KVCacheRequest", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime",
            "StateRequest", "WeightSpec", "build_part", "known_parts", "register_part", "unregister_part"]

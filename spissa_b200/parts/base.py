@@ -33,7 +33,7 @@ import torch
 class WeightSpec:
     """One tensor a part expects in the checkpoint."""
     name: str                 # full checkpoint name
-    shape: tuple
+    shape: tuple              # a negative entry −n: the checkpoint chooses this size (random weights take n)
     kind: str = "float"       # "float" (bfloat16 / float32 storage) or "int" (kept as int32)
     init: str = "normal"      # random-weights mode: "normal" = N(0, std), "ones" = norm weight
 
@@ -65,7 +65,7 @@ class CacheBundle:
     """Several caches for one run of a layer, by name: ``parts`` is a tuple of (name, request) with requests of the
     kinds above (a ``None`` request is left out). The run's view is then a ``BundleView`` whose ``[name]`` is the
     view that the request alone would have got."""
-    parts: tuple
+    parts: tuple              # a request may itself be a ``CacheBundle`` (a mixer made of mixers)
 
     @staticmethod
     def of(**named) -> "CacheBundle":

@@ -21,17 +21,19 @@ class PreNormBlock(Block):
     def __init__(self, mixer, ffn, norms: dict, prefix: str = ""):
         super().__init__(prefix)
         self.mixer = build_part("mixer", mixer)
-        self.ffn = build_part("ffn", ffn)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None      # a layer may have no feed-forward
         self.mixer_norm = build_part("norm", norms["mixer"])
-        self.ffn_norm = build_part("norm", norms["ffn"])
+        self.ffn_norm = build_part("norm", norms["ffn"]) if ffn is not None else None
 
     def children(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
 
     def cache_request(self):
         return self.mixer.cache_request()
 
     def fused_fields(self):
+        if self.ffn is None:
+            return None
         f = dict(kind="prenorm", mixer_norm=self.mixer_norm.fused_fields(), mixer=self.mixer.fused_fields(),
                  ffn_norm=self.ffn_norm.fused_fields(), ffn=self.ffn.fused_fields())
         return None if any(v is None for v in f.values()) else f
@@ -40,6 +42,8 @@ class PreNormBlock(Block):
         with phase("attention_norm_ms"):
             x = self.mixer_norm.forward(h)
         self.mixer.forward(x, step, cache, h)
+        if self.ffn is None:
+            return
         with phase("mlp_norm_ms"):
             x = self.ffn_norm.forward(h)
         self.ffn.forward(x, step, h)
@@ -95,3 +99,81 @@ class ShiftedPreNormBlock(Block):
             with phase("mlp_norm_ms"):
                 x = self.ffn_norm.forward(h)
             self.ffn.forward(x, step, h)
+
+
+@register_part("block", "hyper")
+class HyperConnectionBlock(Block):
+    """The pre-norm arrangement over several residual streams (hyper-connections). A token's row of ``h`` holds
+    ``streams`` copies X_1 … X_S of the stream's width side by side. For each sublayer q (1 the mixer, 2 the
+    feed-forward, which may be absent) with learned coefficients in_q [S], out_q [S] and mix_q [S, S] (from, to):
+
+        a = norm_q(Σ_s in_q[s] X_s);   y = sublayer_q(a);   X_t ← Σ_s mix_q[s, t] X_s + out_q[t] · y   (all t at once)
+
+    The sublayers keep their contract: they ADD into a 32-bit row buffer, which is zero when they get it. One kernel
+    takes y into the streams, leaves the buffer zeroed and norms the next sublayer's input; the norms must describe
+    themselves as layer norms (``fused_fields()`` kind ``layernorm``). ``names``: the tensors' names behind the prefix
+    (``in1``, ``out1``, ``mix1``, ``in2``, ``out2``, ``mix2``)."""
+    graph_safe = True
+    kernel_modules = ("hybrid",)
+
+    def __init__(self, mixer, ffn, norms: dict, hidden_size: int, streams: int, prefix: str = "", names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.streams = int(hidden_size), int(streams)
+        if self.streams < 1:
+            raise ValueError(f"{prefix}: a layer needs at least one stream")
+        self.mixer = build_part("mixer", mixer)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.mixer_norm = build_part("norm", norms["mixer"])
+        self.ffn_norm = build_part("norm", norms["ffn"]) if ffn is not None else None
+        n = dict(in1="hc1.in", out1="hc1.out", mix1="hc1.mix", in2="hc2.in", out2="hc2.out", mix2="hc2.mix")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.coef = {}
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+
+    def weight_specs(self):
+        S = self.streams
+        specs = []
+        for q in ("1", "2") if self.ffn is not None else ("1",):
+            specs += [WeightSpec(self.names["in" + q], (S,), init=f"const:{1.0 / S}"),
+                      WeightSpec(self.names["out" + q], (S,), init="const:1.0"),
+                      WeightSpec(self.names["mix" + q], (S, S), init="eye")]
+        return specs
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        # a handful of numbers per layer; the kernel reads them as 32-bit (exact for either storage type)
+        self.coef = {k: tensors[name].float().contiguous() for k, name in self.names.items() if name in tensors}
+
+    def _layer_norm(self, part) -> dict:
+        f = part.fused_fields()
+        if f is None or f.get("kind") != "layernorm":
+            raise ValueError(f"{self.prefix}: the norms of this arrangement are layer norms")
+        return f
+
+    def forward(self, h, step, cache):
+        S, W, c = self.streams, self.hidden_size, self.coef
+        y = step.scratch.get("sublayer_sum")
+        if y is None or y.shape[1] != W:
+            y = step.scratch["sublayer_sum"] = torch.zeros(h.shape[0], W, dtype=torch.float32, device=h.device)
+        x = torch.empty(h.shape[0], W, dtype=self.rt.act_dtype, device=h.device)
+        n1 = self._layer_norm(self.mixer_norm)
+        with phase("attention_norm_ms"):
+            K.streams_norm(h, S, W, out=x, weight=n1["weight"], eps=n1["eps"], in_coef=c["in1"])
+        self.mixer.forward(x, step, cache, y)
+        if self.ffn is None:
+            with phase("streams_update_ms"):
+                K.streams_norm(h, S, W, y=y, mix=c["mix1"], out_coef=c["out1"])
+            return
+        n2 = self._layer_norm(self.ffn_norm)
+        with phase("streams_update+mlp_norm_ms"):
+            K.streams_norm(h, S, W, out=x, weight=n2["weight"], eps=n2["eps"], y=y, mix=c["mix1"], out_coef=c["out1"],
+                           in_coef=c["in2"])
+        self.ffn.forward(x, step, y)
+        with phase("streams_update_ms"):
+            K.streams_norm(h, S, W, y=y, mix=c["mix2"], out_coef=c["out2"])

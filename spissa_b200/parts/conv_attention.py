@@ -1,0 +1,98 @@
+"""Grouped-query attention whose projections pass a short convolution over time, as a mixer (not in the reference).
+
+    q = conv(x·Wqᵀ), k = conv(x·Wkᵀ), v = conv(x·Wvᵀ)          conv: y_t = Σ_j w[:, j] ⊙ u_{t−taps+1+j} per channel,
+                                                                zeros before the sequence's start, no bias
+    q, k: dim i turns with dim i + r/2 over the first r dims of each head (the position part's ``rotary_dim``)
+    q, k ← q, k / sqrt(mean(·²) + eps) per head                 (``qk_norm_eps`` None: left as they are)
+    score = (q · k) · scale over the visible keys (``window`` None: all earlier ones), softmax in 32-bit
+    y += Wo · concat_h(softmax · v) · out_scale
+
+Keys and values may have different sizes per head (``v_head_dim``). The last taps − 1 projected rows of a sequence are
+its state beside the paged keys and values; the convolution, the rotation and the norm run in 32-bit on the unrounded
+projections in one kernel that also writes the cache (the values already times ``out_scale``). The attention itself is
+the grouped-query mixer's: its tensor-core kernels where key and value sizes agree, else the generic one.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..csrc import lib as K
+from .attention import GQAAttention
+from .base import CacheBundle, KVCacheRequest, StateRequest, WeightSpec
+from .linear import Linear
+from .registry import register_part
+from ..phases import phase
+
+
+@register_part("mixer", "conv_attention")
+class ConvAttention(GQAAttention):
+    graph_safe = True
+    kernel_modules = ("hybrid",)
+    kernel_modules_bf16 = ("attention",)
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int | None = None,
+                 conv_taps: int = 1, scale: float | None = None, qk_norm_eps: float | None = None,
+                 out_scale: float = 1.0, position=None, window=None, prefix: str = "", names: dict | None = None):
+        n = dict(q="q", k="k", v="v", o="o", conv_suffix=".conv")
+        n.update(names or {})
+        self.conv_suffix = n.pop("conv_suffix")
+        super().__init__(hidden_size, num_heads, num_kv_heads, head_dim, position=position, window=window,
+                         prefix=prefix, names=n)
+        self.v_head_dim = int(v_head_dim or head_dim)
+        self.conv_taps = max(1, int(conv_taps or 1))
+        if scale is not None:
+            self.scale = float(scale)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.out_scale = float(out_scale)
+        self.conv = None
+
+    @property
+    def channels(self) -> int:
+        return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.v_head_dim
+
+    def weight_specs(self):
+        H, nh, nkv, d, vd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        shapes = dict(q=(nh * d, H), k=(nkv * d, H), v=(nkv * vd, H))
+        specs = [WeightSpec(self.names[k], s) for k, s in shapes.items()] + [WeightSpec(self.names["o"], (H, nh * vd))]
+        if self.conv_taps > 1:
+            specs += [WeightSpec(self.names[k] + self.conv_suffix, (s[0], self.conv_taps), init="const:0.5")
+                      for k, s in shapes.items()]
+        return specs
+
+    def cache_request(self):
+        vd = self.v_head_dim if self.v_head_dim != self.head_dim else None
+        state = StateRequest((self.conv_taps - 1, self.channels), torch.float32) if self.conv_taps > 1 else None
+        return CacheBundle.of(kv=KVCacheRequest(self.num_kv_heads, self.head_dim, self.window, v_head_dim=vd), conv=state)
+
+    def fused_fields(self):
+        return None
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        if self.conv_taps > 1:
+            self.conv = torch.cat([tensors[self.names[k] + self.conv_suffix] for k in ("q", "k", "v")], dim=0).contiguous()
+
+    def forward(self, x, step, cache, residual):
+        nh, nkv, d, vd = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        kv = cache["kv"]
+        if not kv.writes:
+            raise ValueError(f"{self.prefix}: this mixer writes its own cache")
+        state = cache["conv"].state if self.conv_taps > 1 else None
+        inv_freq, rd = self.position.rotary() if self.position is not None else (None, 0)
+        with phase("qkv_projection_ms"):
+            qkv = self.qkv(x, out_dtype=torch.float32)             # convolution and rotation read unrounded products
+        with phase("conv+rotary+kv_append_ms"):
+            q = torch.empty(x.shape[0], nh * d, dtype=self.rt.act_dtype, device=x.device)
+            K.conv_qk_store(qkv, self.conv, self.conv_taps, state, q, kv.k_pool, kv.v_pool, kv, step, inv_freq, nh, nkv,
+                            d, vd, rd, self.qk_norm_eps or 0.0, v_scale=self.out_scale,
+                            unit_rms=self.qk_norm_eps is not None)
+        with phase("attention_ms"):
+            if vd == d:
+                ctx = self.attend(q, step, kv)
+            else:
+                ctx = torch.empty(x.shape[0], nh * vd, dtype=self.rt.act_dtype, device=x.device)
+                K.attention_generic(q, kv.k_pool, kv.v_pool, ctx, kv, nh, nkv, d, self.window, self.scale, vd=vd)
+        with phase("o_projection+attention_residual_ms"):
+            self.o(ctx, out=residual, accumulate=True)

@@ -6,6 +6,18 @@ reference). The activation runs in 32-bit on the unrounded product.
 
 SwiGLU feed-forward: down( silu(x·Wgᵀ) ⊙ (x·Wuᵀ) ), silu(z) = z / (1 + e^{-z}).
 
+GELU feed-forward: down( gelu(x·Wupᵀ) ) with the tanh form gelu(z) = ½ z (1 + tanh(√(2/π) (z + 0.044715 z³))) (not in
+the reference).
+
+Clamped GLU feed-forward: g = min(x·Wgᵀ, limit), u = clamp(x·Wuᵀ, ±limit), down( g · sigmoid(slope · g) · (u + 1) ) (not
+in the reference).
+
+Routed experts: ``experts`` clamped-GLU feed-forwards of which each token uses ``top``. s = sigmoid(x·Wrᵀ) in 32-bit;
+the choice reads s + correction, the weights read s: the experts form ``groups`` equal groups of neighbours, a group's
+score is the sum of its two largest choice scores, only experts of the ``keep_groups`` best groups can be chosen, the
+``top`` largest choice scores among them are; weight_k = s_k / (Σ s_k + 1e-20); y += Σ_k weight_k · expert_k(x), plus a
+shared expert that every token uses (not in the reference).
+
 crates/spissa-runtime/src/models/llama/generate.rs:590-637 (gate, up), :642-763 (down);
 crates/spissa-runtime/src/ops.rs:192-194 (silu). Gate and up run as one matrix product
 over the stacked weight [Wg; Wu]; the down projection adds into the residual stream.
@@ -17,7 +29,7 @@ import torch
 from ..csrc import lib as K
 from .base import FeedForward, WeightSpec
 from .linear import GatedLinear, Linear
-from .registry import register_part
+from .registry import build_part, register_part
 from ..phases import phase
 
 
@@ -92,3 +104,133 @@ class PolyNormMLP(FeedForward):
             K.polynorm(z, self.coef, act, self.eps)
         with phase("down_projection+mlp_residual_ms"):
             self.down(act, out=residual, accumulate=True)
+
+
+@register_part("ffn", "gelu_mlp")
+class GeluMLP(FeedForward):
+    graph_safe = True
+    kernel_modules = ("hybrid",)
+
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "", names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        n = dict(up="up", down="down")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.up = self.down = None
+
+    def weight_specs(self):
+        H, I = self.hidden_size, self.intermediate_size
+        return [WeightSpec(self.names["up"], (I, H)), WeightSpec(self.names["down"], (H, I))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.up = Linear(tensors[self.names["up"]])
+        self.down = Linear(tensors[self.names["down"]])
+
+    def forward(self, x, step, residual):
+        with phase("up_projection_ms"):
+            z = self.up(x, out_dtype=torch.float32)                # the activation reads unrounded products
+        with phase("activation_ms"):
+            act = torch.empty(x.shape[0], self.intermediate_size, dtype=self.rt.act_dtype, device=x.device)
+            K.gelu_tanh(z, act)
+        with phase("down_projection+mlp_residual_ms"):
+            self.down(act, out=residual, accumulate=True)
+
+
+@register_part("ffn", "clamped_glu")
+class ClampedGLU(FeedForward):
+    graph_safe = True
+    kernel_modules = ("hybrid",)
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, slope: float = 1.702, prefix: str = "",
+                 names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.slope = float(limit), float(slope)
+        n = dict(gate="gate", up="up", down="down")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.gate_up = self.down = None
+
+    def weight_specs(self):
+        H, I = self.hidden_size, self.intermediate_size
+        return [WeightSpec(self.names["gate"], (I, H)), WeightSpec(self.names["up"], (I, H)),
+                WeightSpec(self.names["down"], (H, I))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.gate_up = Linear(torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]], dim=0))
+        self.down = Linear(tensors[self.names["down"]])
+
+    def forward(self, x, step, residual):
+        with phase("gate_projection+up_projection_ms"):
+            gu = self.gate_up(x, out_dtype=torch.float32)
+        with phase("activation_ms"):
+            act = torch.empty(x.shape[0], self.intermediate_size, dtype=self.rt.act_dtype, device=x.device)
+            K.clamped_glu(gu, act, self.limit, self.slope)
+        with phase("down_projection+mlp_residual_ms"):
+            self.down(act, out=residual, accumulate=True)
+
+
+@register_part("ffn", "routed_experts")
+class RoutedExperts(FeedForward):
+    """``shared``: a feed-forward part (any kind) that every token uses besides its experts, or None. Tensor names:
+    expert i's tensors stand under ``expert_prefix`` + i + "." (``e0.gate`` …)."""
+    graph_safe = True
+    kernel_modules = ("hybrid",)
+
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: float,
+                 slope: float = 1.702, groups: int = 1, keep_groups: int = 1, shared=None, prefix: str = "",
+                 names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.experts, self.top = int(experts), int(top)
+        self.groups, self.keep_groups = max(1, int(groups or 1)), int(keep_groups or 1)
+        self.limit, self.slope = float(limit), float(slope)
+        if self.experts % self.groups:
+            raise ValueError(f"{prefix}: {self.experts} experts do not form {self.groups} equal groups")
+        allowed = self.experts if self.groups == 1 else self.keep_groups * (self.experts // self.groups)
+        if not (1 <= self.top <= allowed):
+            raise ValueError(f"{prefix}: {self.top} experts cannot be chosen among {allowed} allowed")
+        n = dict(router="router", correction="correction", expert_prefix="e", gate="gate", up="up", down="down")
+        n.update(names or {})
+        self.names = n
+        self.shared = build_part("ffn", shared) if shared is not None else None
+        self.router = self.correction = self.w_gate_up = self.w_down = None
+
+    def _expert(self, i: int, which: str) -> str:
+        return f"{self.prefix}{self.names['expert_prefix']}{i}.{self.names[which]}"
+
+    def children(self):
+        return [self.shared] if self.shared is not None else []
+
+    def weight_specs(self):
+        H, I = self.hidden_size, self.intermediate_size
+        specs = [WeightSpec(self.prefix + self.names["router"], (self.experts, H)),
+                 WeightSpec(self.prefix + self.names["correction"], (self.experts,))]
+        for i in range(self.experts):
+            specs += [WeightSpec(self._expert(i, "gate"), (I, H)), WeightSpec(self._expert(i, "up"), (I, H)),
+                      WeightSpec(self._expert(i, "down"), (H, I))]
+        return specs
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.router = Linear(tensors[self.prefix + self.names["router"]])
+        self.correction = tensors[self.prefix + self.names["correction"]].contiguous()
+        # [E, 2I, H]: an expert's gate rows, then its up rows; [E, H, I]
+        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]], dim=0)
+                                      for i in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(i, "down")] for i in range(self.experts)]).contiguous()
+
+    def forward(self, x, step, residual):
+        T = x.shape[0]
+        with phase("router_ms"):
+            z = self.router(x, out_dtype=torch.float32)
+            ids = torch.empty(T, self.top, dtype=torch.int32, device=x.device)
+            wts = torch.empty(T, self.top, dtype=torch.float32, device=x.device)
+            K.moe_select(z, self.correction, ids, wts, self.top, self.groups, self.keep_groups)
+        with phase("experts_ms"):
+            K.moe_experts(x, ids, wts, self.w_gate_up, self.w_down, residual, self.top, self.limit, self.slope)
+        if self.shared is not None:
+            self.shared.forward(x, step, residual)

@@ -6,6 +6,10 @@ directly, no ``1 + w``).
 
 Dynamic tanh: y = tanh(alpha · x) ⊙ w + b with a learned scalar alpha: a norm that takes
 no mean and no variance, so a token's row needs no reduction (not in the reference).
+
+Layer norm: y = (x − mean) / sqrt(var + eps) ⊙ w with var the mean of the squared deviations, a weight and no bias
+(not in the reference). Where a model keeps several copies of the residual stream side by side in a row
+(``streams``), the norm reads their sum.
 """
 from __future__ import annotations
 
@@ -81,4 +85,36 @@ class DynamicTanh(Norm):
         n = h.shape[0] if rows is None else rows.shape[0]
         out = torch.empty(n, self.size, dtype=self.rt.act_dtype, device=h.device)
         K.dyt_norm(h, self.weight, self.bias, self.alpha, out, rows)
+        return out
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """``streams`` > 1: a row of ``h`` holds that many streams of ``size`` one after another and the norm reads their
+    sum (how the final norm of a model with several residual streams takes them in)."""
+    graph_safe = True
+    kernel_modules = ("hybrid",)
+
+    def __init__(self, size: int, eps: float, prefix: str = "", weight_name: str = "weight", streams: int = 1):
+        super().__init__(prefix)
+        self.size, self.eps, self.streams = int(size), float(eps), int(streams)
+        self.weight_name = prefix + weight_name
+        self.weight = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.weight_name, (self.size,), init="ones")]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors[self.weight_name].contiguous()
+
+    def fused_fields(self):
+        if self.weight is None:
+            return None
+        return dict(kind="layernorm", weight=self.weight, eps=self.eps, size=self.size)
+
+    def forward(self, h: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        n = h.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty(n, self.size, dtype=self.rt.act_dtype, device=h.device)
+        K.streams_norm(h, self.streams, self.size, out=out, weight=self.weight, eps=self.eps, rows=rows)
         return out

@@ -112,8 +112,9 @@ def check_against(source: TensorSource, specs: list) -> None:
             continue
         s = want[n]
         shape, dt = source.shape(n), source.dtype_name(n)
-        if tuple(shape) != tuple(s.shape):
-            mismatched.append(f"{n}: file has {list(shape)}, model wants {list(s.shape)}")
+        if len(shape) != len(s.shape) or any(b >= 0 and a != b for a, b in zip(shape, s.shape)):
+            wants = [b if b >= 0 else "any" for b in s.shape]
+            mismatched.append(f"{n}: file has {list(shape)}, model wants {wants}")
         elif s.kind == "float" and dt not in _FLOAT:
             mismatched.append(f"{n}: stored as {dt}, a floating tensor (BF16, F16, F32) is wanted")
         elif s.kind == "int" and dt not in _INT:

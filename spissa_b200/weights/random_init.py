@@ -22,10 +22,16 @@ def random_tensors(specs: list, seed: int, std: float = 0.02, norm_std: float = 
     gen.manual_seed(int(seed))
     out = {}
     for s in sorted({s.name: s for s in specs}.values(), key=lambda s: s.name):
+        if any(n < 0 for n in s.shape):                # a size the checkpoint is free to choose: −n stands for "n here"
+            s = type(s)(s.name, tuple(abs(n) for n in s.shape), s.kind, s.init)
         if s.kind == "int":
             out[s.name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
         elif s.init.startswith("const:"):              # a fixed value (a scalar or a table that must not be random)
             out[s.name] = torch.full(s.shape, float(s.init[6:]), dtype=torch.float32, device=device).to(dtype)
+        elif s.init == "eye":                          # a square table that starts as "everything keeps itself", plus noise
+            t = torch.eye(s.shape[0], dtype=torch.float32, device=device)
+            t = t + (norm_std or std) * torch.randn(s.shape, generator=gen, dtype=torch.float32, device=device)
+            out[s.name] = t.to(dtype)
         elif s.init == "ones":
             t = torch.ones(s.shape, dtype=torch.float32, device=device)
             if norm_std > 0:
