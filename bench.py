@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b] [--batch B]
                     [--context T] [--profile-phases]
     python bench.py --design duzinex [--design-sizes 1k,2k,4k]      (the Duzinex decoder beside Llama at equal sizes)
+    python bench.py --design gozatar [--design-sizes 1k,2k,4k]      (the Gozatar decoder likewise)
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 from prompts of
 about 2,048 tokens in a cache of 4,096 tokens per sequence, timed on the device with CUDA
@@ -203,6 +204,32 @@ def llama_config_like(size: dict, layers: int) -> dict:
                 rms_norm_eps=1e-6, max_position_embeddings=131072)
 
 
+# --design gozatar: eight layers of a sliding-window attention (window 1,024, a convolution of four taps, half of each
+# head rotated) beside a gated linear attention (heads of 128 x 256); the first and fifth layers have a dense feed-forward
+# of ``ff``, the others 32 experts of ff/4 of which a token uses 4 (from 2 of 4 groups) plus a shared expert of ff/4: a
+# token's active feed-forward weights are 1.25 times the dense layer's (three matrices instead of two).
+GOZATAR_SIZES = {
+    "1k": dict(left=(8, 2, 128), right=(4, 128, 256)),
+    "2k": dict(left=(16, 4, 128), right=(8, 128, 256)),
+    "4k": dict(left=(32, 8, 128), right=(16, 128, 256)),
+}
+GOZATAR_LAYERS = 8
+
+
+def gozatar_config(size: dict, goz: dict, window: int = DESIGN_WINDOW) -> dict:
+    W, ff = size["width"], size["ff"]
+    h, g, d = goz["left"]
+    rh, rd, rvd = goz["right"]
+    mixer = dict(left=dict(heads=h, kv_heads=g, dim=d, vdim=d, conv=4, scale=d ** -0.5, mask=dict(size=window),
+                           rot=dict(dims=d // 2, base=10000.0)), left_scale=0.7,
+                 right=dict(heads=rh, dim=rd, vdim=rvd, tau=16.0, rank=16), right_scale=0.7)
+    moe = dict(kind="moe", expert=dict(ff=ff // 4, limit=7.0), shared=dict(ff=ff // 4, limit=7.0),
+               router=dict(experts=32, top=4, groups=dict(count=4, keep=2)))
+    layers = [dict(type="parallel", mixer=mixer, mlp=dict(kind="dense", ff=ff) if i % 4 == 0 else moe)
+              for i in range(GOZATAR_LAYERS)]
+    return dict(architecture="Gozatar", vocab=DESIGN_VOCAB, width=W, streams=2, norm=dict(eps=1e-6), layers=layers)
+
+
 def design_compare(args) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8 behind such prompts) of the Duzinex decoder and of the
     Llama decoder with the same width, feed-forward size and number of layer runs; per-phase device times of both
@@ -215,15 +242,16 @@ def design_compare(args) -> int:
     peaks = load_peaks()
     torch.cuda.set_device(0)
     T, B = PREFILL_TOKENS, 8
-    out = {"design": "duzinex", "beside": "llama", "dtype": args.dtype, "prefill_tokens": T, "decode_batch": B,
+    design = args.design
+    out = {"design": design, "beside": "llama", "dtype": args.dtype, "prefill_tokens": T, "decode_batch": B,
            "window": DESIGN_WINDOW, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops", "source")}, "sizes": {}}
     names = [n for n in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES) if n in DESIGN_SIZES]
     for name in names:
         size = DESIGN_SIZES[name]
-        dz = duzinex_config(size)
+        dz = duzinex_config(size) if design == "duzinex" else gozatar_config(size, GOZATAR_SIZES[name])
         runs = len(config_from_dict(dz).to_spec().schedule)
         row = {}
-        for label, cfg_dict in (("duzinex", dz), ("llama", llama_config_like(size, runs))):
+        for label, cfg_dict in ((design, dz), ("llama", llama_config_like(size, runs))):
             cfg = config_from_dict(cfg_dict)
             engine = Engine.from_config(cfg, seed=0, dtype=args.dtype, max_tokens=B * (T + 128), max_seqs=B, device="cuda:0")
             rng = random.Random(7)
@@ -291,7 +319,9 @@ def design_compare(args) -> int:
                               decode_phases_ms={k: round(v, 4) for k, v in sorted(dec_phases.items())})
             del engine
             torch.cuda.empty_cache()
-        row["rooflines"] = design_rooflines(size, row, T, B, peaks, 4 if args.dtype == "float32" else 2)
+        eb = 4 if args.dtype == "float32" else 2
+        row["rooflines"] = (design_rooflines(size, row, T, B, peaks, eb) if design == "duzinex"
+                            else gozatar_rooflines(size, GOZATAR_SIZES[name], row, T, peaks, eb))
         out["sizes"][name] = row
     print(json.dumps(out))
     return 0
@@ -341,6 +371,42 @@ def design_rooflines(size, row, T, B, peaks, eb) -> dict:
     out["polynorm (hbm)"] = dict(ms=dz.get("activation_ms"), frac=frac(10 * T * ff * (4.0 + eb), bw, dz.get("activation_ms")))
     out["norm+shift (hbm)"] = dict(ms=dz.get("mixer_norm+shift_ms"), frac=frac(10 * T * W * (4.0 + eb), bw, dz.get("mixer_norm+shift_ms")))
     out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    return out
+
+
+def gozatar_rooflines(size, goz, row, T, peaks, eb) -> dict:
+    """The same for the Gozatar decoder's kernel groups of a prompt step (sums over its eight layers)."""
+    W, ff = size["width"], size["ff"]
+    h, g, d = goz["left"]
+    rh, rd, rvd = goz["right"]
+    nh, nkv, hd = size["llama"]
+    gz, ll = row["gozatar"]["prefill_phases_ms"], row["llama"]["prefill_phases_ms"]
+    tf, bw = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    L, n_moe = GOZATAR_LAYERS, GOZATAR_LAYERS - GOZATAR_LAYERS // 4
+    win = min(T, DESIGN_WINDOW)
+    pairs = T * win - win * (win - 1) / 2
+    frac = lambda work, peak, ms: round(work / (ms * 1e-3) / peak, 4) if ms else None
+    out = {}
+    out["window attention (tensor)"] = dict(ms=gz.get("attention_ms"), frac=frac(L * 4.0 * pairs * d * h, tf, gz.get("attention_ms")))
+    ll_att, ll_runs = ll.get("attention_ms"), row["llama"]["layer_runs"]
+    out["llama attention (tensor)"] = dict(ms=ll_att, frac=frac(ll_runs * 4.0 * (T * (T + 1) / 2) * hd * nh, tf, ll_att))
+    # the recurrence's 2·2·d·vd FLOPs per token and head (the least any form does), and its 32-bit operands and output
+    out["gla (tensor)"] = dict(ms=gz.get("gla_ms"), frac=frac(L * T * rh * 4.0 * rd * rvd, tf, gz.get("gla_ms")))
+    out["gla (hbm)"] = dict(ms=gz.get("gla_ms"),
+                            frac=frac(L * T * ((2 * rh * rd + 2 * rh * rvd + 16) * 4.0 + rh * rvd * eb), bw, gz.get("gla_ms")))
+    # the experts: 4 of 32 per token, three matrices of W x ff/4 each
+    out["experts (tensor)"] = dict(ms=gz.get("experts_ms"), frac=frac(n_moe * T * 4 * 3 * 2.0 * W * (ff // 4), tf, gz.get("experts_ms")))
+    ll_ff = (ll.get("gate_projection+up_projection+activation_multiply_ms") or 0) + (ll.get("down_projection+mlp_residual_ms") or 0)
+    out["llama feed-forward (tensor)"] = dict(ms=ll_ff, frac=frac(ll_runs * T * 3 * 2.0 * W * ff, tf, ll_ff))
+    C = (h + g) * d + g * d
+    out["conv+rotary+store (hbm)"] = dict(ms=gz.get("conv+rotary+kv_append_ms"),
+                                          frac=frac(L * T * C * (4.0 + eb), bw, gz.get("conv+rotary+kv_append_ms")))
+    norm_ms = (gz.get("attention_norm_ms") or 0) + (gz.get("streams_update+mlp_norm_ms") or 0) + (gz.get("streams_update_ms") or 0)
+    # per layer: the streams read once for the first norm, read and written by each of the two updates, y read twice
+    out["streams+norm (hbm)"] = dict(ms=norm_ms, frac=frac(L * T * W * (2 * 4.0 + 2 * (4 * 4.0 + 4.0) + 2 * eb), bw, norm_ms))
+    out["llama norm (hbm)"] = dict(ms=ll.get("attention_norm_ms"), frac=frac(ll_runs * T * W * (4.0 + eb), bw, ll.get("attention_norm_ms")))
+    act_ms = gz.get("activation_ms")
+    out["activations (hbm)"] = dict(ms=act_ms, frac=frac((2 * T * ff + n_moe * T * 3 * (ff // 4)) * (4.0 + eb) * 1.0, bw, act_ms))
     return out
 
 
@@ -705,7 +771,7 @@ def main() -> int:
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
                          "gemv_down|gemv_head|diff_flash|diff_decode|retention_chunks|retention_step|mingru_chunks|polynorm|token_shift|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
-    ap.add_argument("--design", default=None, choices=["duzinex"],
+    ap.add_argument("--design", default=None, choices=["duzinex", "gozatar"],
                     help="measure this design beside the Llama decoder at equal layer sizes instead of the headline workload")
     ap.add_argument("--design-sizes", default="", dest="design_sizes", help="which of 1k,2k,4k (default: all)")
     ap.add_argument("--reps", type=int, default=20)

@@ -18,6 +18,7 @@
 // fast-math); stores round to the activation type. States are 32-bit. Every output row is reduced in an order that
 // depends on its own sequence only, never on the batch or on how the tokens were cut into steps.
 #include "common.cuh"
+#include "flash_common.cuh"
 
 SP_API const char* sp_hybrid_last_error() { return sp_error_text; }
 SP_DEFINE_RANGE_API(hybrid)
@@ -456,6 +457,292 @@ __global__ void __launch_bounds__(256) gla_step_kernel(GlaArgs a) {
     }
 }
 
+// ---- prompts: chunks of GLC tokens, all chunks in parallel. Within a chunk, with B_i = Σ_{u ≤ i} log α_u per key
+// channel (counted from the chunk's first token):
+//     o_i   = (q_i ⊙ e^{B_i}) · S₀  +  Σ_{j ≤ i} P_ij v_j,      P_ij = Σ_e q_ie k_je e^{B_ie − B_je}
+//     S_end = diag(e^{B_last}) S₀  +  Σ_j (k_j ⊙ e^{B_last − B_j}) v_jᵀ
+// Every exponent is ≤ 0, so nothing overflows whatever the decays are. Five launches: (1) per (chunk, head) the decays'
+// running sums, q ⊙ e^{B}, k ⊙ e^{B_last − B}, e^{B_last} and P; (2) every chunk's own Σ_j (…) v_jᵀ; (3) per (sequence,
+// head) the chunks' start states one after the other, element by element, the last one becomes the slot's state;
+// (4) every chunk's outputs from its start state; (5) the norm, the gate, the store. A chunk's arithmetic depends on
+// where the chunk starts in its step only. Products are tiles out[m][n] = Σ_k a[k][m]·b[k][n] from shared memory,
+// k-major, 16 x 16 threads owning 4·MA x 4 outputs each.
+#define GLC 64
+#define GLC_TS 68              // row stride of arrays that are 64 tokens wide
+
+struct GlcArgs {
+    GlaArgs g;
+    float* qe; float* ke;      // [T][H·d]
+    float* dl;                 // [chunks][H][d]  e^{B_last}
+    float* pt;                 // [chunks][H][64][64]  P transposed: pt[j][i]
+    float* cs;                 // [chunks][H][d][vd]: (2) the chunk's own sum, (3) turns it into its start state
+    int n_chunks;
+};
+
+__device__ __forceinline__ bool glc_chunk_of(const GlaArgs& a, int x, int& s, int& t0, int& n) {
+    for (s = 0; s < a.B; ++s) {
+        const int first = a.seq_start[s], cnt = a.seq_start[s + 1] - first;
+        const int nc = (cnt + GLC - 1) / GLC;
+        if (x < nc) {
+            t0 = first + x * GLC;
+            n = min(GLC, cnt - x * GLC);
+            return true;
+        }
+        x -= nc;
+    }
+    return false;
+}
+
+template <int MA>
+__device__ __forceinline__ void glc_mm(const float* __restrict__ a, int lda, const float* __restrict__ b, int ldb, int K,
+                                       float (&acc)[4 * MA][4], int ty, int tx) {
+    for (int k = 0; k < K; ++k) {
+        const float4 bv = *(const float4*)(b + (size_t)k * ldb + 4 * tx);
+        const float bn[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int i = 0; i < MA; ++i) {
+            const float4 av = *(const float4*)(a + (size_t)k * lda + 4 * ty + 64 * i);
+            const float am[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int v = 0; v < 4; ++v) acc[4 * i + u][v] = fmaf(am[u], bn[v], acc[4 * i + u][v]);
+        }
+    }
+}
+
+// (1) grid (chunks, H)
+__global__ void __launch_bounds__(256) gla_chunk_prep_kernel(GlcArgs c) {
+    extern __shared__ __align__(16) float sm[];
+    const GlaArgs& a = c.g;
+    const int d = a.d, rank = a.rank;
+    float* qT = sm;                           // [d][GLC_TS]  q/√d
+    float* kT = qT + (size_t)d * GLC_TS;      // [d][GLC_TS]
+    float* bT = kT + (size_t)d * GLC_TS;      // [d][GLC_TS]  B
+    float* rr = bT + (size_t)d * GLC_TS;      // [GLC][rank]
+    float* A2 = rr + (size_t)GLC * rank;      // [d][rank]
+    int s, t0, n;
+    if (!glc_chunk_of(a, blockIdx.x, s, t0, n)) return;
+    const int h = blockIdx.y;
+    const int Hd = a.H * d, Hv = a.H * a.vd;
+    const float qscale = 1.0f / sqrtf((float)d);
+    for (int e = threadIdx.x; e < n * rank; e += blockDim.x) rr[e] = a.proj[(size_t)(t0 + e / rank) * a.ld + 2 * Hd + 2 * Hv + e % rank];
+    for (int e = threadIdx.x; e < d * rank; e += blockDim.x) A2[e] = sp_ld_dt(a.a2, a.w_dt, (size_t)h * d * rank + e);
+    for (int x = threadIdx.x; x < GLC * d; x += blockDim.x) {
+        const int i = x / d, e = x % d;
+        const bool in = i < n;
+        const float* row = a.proj + (size_t)(t0 + (in ? i : 0)) * a.ld;
+        qT[e * GLC_TS + i] = in ? row[h * d + e] * qscale : 0.0f;
+        kT[e * GLC_TS + i] = in ? row[Hd + h * d + e] : 0.0f;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+        const float bias = sp_ld_dt(a.a2b, a.w_dt, h * d + e);
+        float run = 0.0f;
+        for (int i = 0; i < GLC; ++i) {
+            if (i < n) {
+                float z = bias;
+                for (int r = 0; r < rank; ++r) z = fmaf(A2[e * rank + r], rr[i * rank + r], z);
+                run += (fminf(z, 0.0f) - log1pf(expf(-fabsf(z)))) * a.inv_tau;
+            }
+            bT[e * GLC_TS + i] = run;                            // beyond the chunk's tokens: B_last
+        }
+    }
+    __syncthreads();
+    // P: thread (ty, tx) owns pairs i = 4ty … 4ty+3, j = 4tx … 4tx+3; blocks above the diagonal stay zero
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float p[4][4] = {};
+    if (tx <= ty) {
+        for (int e = 0; e < d; ++e) {
+            const float4 q4 = *(const float4*)(qT + e * GLC_TS + 4 * ty), bi4 = *(const float4*)(bT + e * GLC_TS + 4 * ty);
+            const float4 k4 = *(const float4*)(kT + e * GLC_TS + 4 * tx), bj4 = *(const float4*)(bT + e * GLC_TS + 4 * tx);
+            const float qi[4] = {q4.x, q4.y, q4.z, q4.w}, bi[4] = {bi4.x, bi4.y, bi4.z, bi4.w};
+            const float kj[4] = {k4.x, k4.y, k4.z, k4.w}, bj[4] = {bj4.x, bj4.y, bj4.z, bj4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    if (4 * tx + v <= 4 * ty + u) p[u][v] = fmaf(qi[u] * kj[v], expf(bi[u] - bj[v]), p[u][v]);
+        }
+    }
+    float* pt = c.pt + ((size_t)blockIdx.x * a.H + h) * GLC * GLC;
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+        *(float4*)(pt + (size_t)(4 * tx + v) * GLC + 4 * ty) = make_float4(p[0][v], p[1][v], p[2][v], p[3][v]);
+    // q ⊙ e^{B}, k ⊙ e^{B_last − B}, e^{B_last}
+    for (int x = threadIdx.x; x < n * d; x += blockDim.x) {
+        const int i = x / d, e = x % d;
+        const float b = bT[e * GLC_TS + i], bl = bT[e * GLC_TS + GLC - 1];
+        c.qe[(size_t)(t0 + i) * Hd + h * d + e] = qT[e * GLC_TS + i] * expf(b);
+        c.ke[(size_t)(t0 + i) * Hd + h * d + e] = kT[e * GLC_TS + i] * expf(bl - b);
+    }
+    for (int e = threadIdx.x; e < d; e += blockDim.x) c.dl[((size_t)blockIdx.x * a.H + h) * d + e] = expf(bT[e * GLC_TS + GLC - 1]);
+}
+
+// (2) grid (chunks, H, column blocks of 64); MA = ceil(d / 64)
+template <int MA>
+__global__ void __launch_bounds__(256) gla_chunk_sum_kernel(GlcArgs c) {
+    extern __shared__ __align__(16) float sm[];
+    const GlaArgs& a = c.g;
+    const int DP = 64 * MA, d = a.d, vd = a.vd;
+    float* kd = sm;                    // [64][DP]
+    float* vv = kd + GLC * DP;         // [64][64]
+    int s, t0, n;
+    if (!glc_chunk_of(a, blockIdx.x, s, t0, n)) return;
+    const int h = blockIdx.y, c0 = blockIdx.z * 64;
+    const int Hd = a.H * d, Hv = a.H * vd;
+    for (int x = threadIdx.x; x < GLC * DP; x += blockDim.x) {
+        const int j = x / DP, e = x % DP;
+        kd[x] = (j < n && e < d) ? c.ke[(size_t)(t0 + j) * Hd + h * d + e] : 0.0f;
+    }
+    for (int x = threadIdx.x; x < GLC * 64; x += blockDim.x) {
+        const int j = x / 64, col = c0 + x % 64;
+        vv[x] = (j < n && col < vd) ? a.proj[(size_t)(t0 + j) * a.ld + 2 * Hd + h * vd + col] : 0.0f;
+    }
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[4 * MA][4] = {};
+    glc_mm<MA>(kd, DP, vv, 64, GLC, acc, ty, tx);
+    float* out = c.cs + ((size_t)blockIdx.x * a.H + h) * d * vd;
+#pragma unroll
+    for (int i = 0; i < MA; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = 4 * ty + 64 * i + u;
+            if (e >= d) continue;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+                if (c0 + 4 * tx + v < vd) out[(size_t)e * vd + c0 + 4 * tx + v] = acc[4 * i + u][v];
+        }
+}
+
+// (3) grid (sequences, H, blocks of 256 state elements)
+__global__ void __launch_bounds__(256) gla_chunk_scan_kernel(GlcArgs c) {
+    const GlaArgs& a = c.g;
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int x = blockIdx.z * 256 + threadIdx.x;
+    if (x >= a.d * a.vd) return;
+    const int slot = a.seq_slot[s];
+    if (slot < 0 || slot >= a.n_slots) return;
+    int first_chunk = 0;
+    for (int b = 0; b < s; ++b) first_chunk += (a.seq_start[b + 1] - a.seq_start[b] + GLC - 1) / GLC;
+    const int nc = (a.seq_start[s + 1] - a.seq_start[s] + GLC - 1) / GLC;
+    float* st = a.state + ((size_t)slot * a.H + h) * a.d * a.vd + x;
+    float S = *st;
+    const int e = x / a.vd;
+    for (int k = 0; k < nc; ++k) {
+        float* slot_k = c.cs + ((size_t)(first_chunk + k) * a.H + h) * a.d * a.vd + x;
+        const float own = *slot_k;
+        *slot_k = S;
+        S = fmaf(c.dl[((size_t)(first_chunk + k) * a.H + h) * a.d + e], S, own);
+    }
+    *st = S;
+}
+
+// (4) grid (chunks, H, column blocks of 64)
+template <int MA>
+__global__ void __launch_bounds__(256) gla_chunk_out_kernel(GlcArgs c) {
+    extern __shared__ __align__(16) float sm[];
+    const GlaArgs& a = c.g;
+    const int DP = 64 * MA, d = a.d, vd = a.vd;
+    float* qT = sm;                          // [DP][GLC_TS]
+    float* S = qT + (size_t)DP * GLC_TS;     // [DP][64]
+    float* pT = S + (size_t)DP * 64;         // [64][64]
+    float* vv = pT + GLC * 64;               // [64][64]
+    int s, t0, n;
+    if (!glc_chunk_of(a, blockIdx.x, s, t0, n)) return;
+    const int h = blockIdx.y, c0 = blockIdx.z * 64;
+    const int Hd = a.H * d, Hv = a.H * vd;
+    for (int x = threadIdx.x; x < GLC * DP; x += blockDim.x) {
+        const int i = x / DP, e = x % DP;
+        qT[e * GLC_TS + i] = (i < n && e < d) ? c.qe[(size_t)(t0 + i) * Hd + h * d + e] : 0.0f;
+    }
+    const float* cs = c.cs + ((size_t)blockIdx.x * a.H + h) * d * vd;
+    for (int x = threadIdx.x; x < DP * 64; x += blockDim.x) {
+        const int e = x / 64, col = c0 + x % 64;
+        S[x] = (e < d && col < vd) ? cs[(size_t)e * vd + col] : 0.0f;
+    }
+    const float* pt = c.pt + ((size_t)blockIdx.x * a.H + h) * GLC * GLC;
+    for (int x = threadIdx.x; x < GLC * 64; x += blockDim.x) {
+        const int j = x / 64, col = c0 + x % 64;
+        pT[x] = pt[x];
+        vv[x] = (j < n && col < vd) ? a.proj[(size_t)(t0 + j) * a.ld + 2 * Hd + h * vd + col] : 0.0f;
+    }
+    __syncthreads();
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[4][4] = {};
+    glc_mm<1>(qT, GLC_TS, S, 64, d, acc, ty, tx);
+    glc_mm<1>(pT, 64, vv, 64, GLC, acc, ty, tx);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = 4 * ty + u;
+        if (i >= n) continue;
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            if (c0 + 4 * tx + v < vd) a.o_raw[(size_t)(t0 + i) * Hv + h * vd + c0 + 4 * tx + v] = acc[u][v];
+    }
+}
+
+// every region of the scratch starts on 16 bytes (the tiles are stored four floats at a time)
+static inline long long glc_up4(long long n) { return (n + 3) / 4 * 4; }
+
+SP_API int sp_gla_chunk_tokens() { return GLC; }
+SP_API int sp_gla_chunked_supported(int d, int vd, int rank) { return d > 0 && d <= 128 && vd > 0 && rank > 0 && rank <= 64; }
+// floats of scratch the chunked form needs (the raw outputs included)
+SP_API long long sp_gla_chunked_scratch_floats(int n_chunks, int T, int H, int d, int vd) {
+    return 2LL * glc_up4((long long)T * H * d) + glc_up4((long long)n_chunks * H * d) + (long long)n_chunks * H * GLC * GLC +
+           glc_up4((long long)n_chunks * H * d * vd) + (long long)T * H * vd;
+}
+
+static SpPerDevice gla_chunk_ready;
+
+SP_API int sp_gla_chunked(const float* proj, int ld, float* state, int n_slots, const void* a2, const void* a2b,
+                          const void* nw, int w_dt, float* scratch, void* out, int out_dt, const int* seq_start,
+                          const int* seq_slot, int B, int T, int n_chunks, int H, int d, int vd, int rank, float tau,
+                          float eps, float out_scale, cudaStream_t stream) {
+    if (B <= 0 || T <= 0) return 0;
+    if (!sp_gla_chunked_supported(d, vd, rank)) SP_FAIL("gla (chunks): sizes d %d, vd %d, rank %d are outside this kernel's range", d, vd, rank);
+    if (!(tau > 0.0f)) SP_FAIL("gla: tau must be positive");
+    GlcArgs c;
+    c.g = GlaArgs{proj, ld, state, n_slots, a2, a2b, nw, w_dt, nullptr, out, out_dt, seq_start, seq_slot, B, H, d, vd, rank,
+                  1.0f / tau, eps, out_scale};
+    c.qe = scratch;
+    if (((uintptr_t)scratch) & 15) SP_FAIL("gla (chunks): the scratch must start on 16 bytes");
+    c.ke = c.qe + glc_up4((long long)T * H * d);
+    c.dl = c.ke + glc_up4((long long)T * H * d);
+    c.pt = c.dl + glc_up4((long long)n_chunks * H * d);
+    c.cs = c.pt + (size_t)n_chunks * H * GLC * GLC;
+    c.g.o_raw = c.cs + glc_up4((long long)n_chunks * H * d * vd);
+    c.n_chunks = n_chunks;
+    const int MA = d <= 64 ? 1 : 2, DP = 64 * MA;
+    const size_t smem1 = (3 * (size_t)d * GLC_TS + (size_t)GLC * rank + (size_t)d * rank) * sizeof(float);
+    const size_t smem2 = ((size_t)GLC * DP + GLC * 64) * sizeof(float);
+    const size_t smem4 = ((size_t)DP * GLC_TS + (size_t)DP * 64 + 2 * GLC * 64) * sizeof(float);
+    if (!gla_chunk_ready.done()) {
+        if (cudaFuncSetAttribute(gla_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(gla_chunk_sum_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(gla_chunk_sum_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(gla_chunk_out_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(gla_chunk_out_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            SP_FAIL("gla (chunks): cannot raise the shared memory limit");
+        gla_chunk_ready.mark();
+    }
+    const int vb = (vd + 63) / 64;
+    gla_chunk_prep_kernel<<<dim3(n_chunks, H), 256, smem1, stream>>>(c);
+    SP_CHECK_LAUNCH("gla_chunk_prep");
+    if (MA == 1) gla_chunk_sum_kernel<1><<<dim3(n_chunks, H, vb), 256, smem2, stream>>>(c);
+    else gla_chunk_sum_kernel<2><<<dim3(n_chunks, H, vb), 256, smem2, stream>>>(c);
+    SP_CHECK_LAUNCH("gla_chunk_sum");
+    gla_chunk_scan_kernel<<<dim3(B, H, (d * vd + 255) / 256), 256, 0, stream>>>(c);
+    SP_CHECK_LAUNCH("gla_chunk_scan");
+    if (MA == 1) gla_chunk_out_kernel<1><<<dim3(n_chunks, H, vb), 256, smem4, stream>>>(c);
+    else gla_chunk_out_kernel<2><<<dim3(n_chunks, H, vb), 256, smem4, stream>>>(c);
+    SP_CHECK_LAUNCH("gla_chunk_out");
+    gla_finish_kernel<<<dim3(T, H), 128, 0, stream>>>(c.g);
+    SP_CHECK_LAUNCH("gla_finish");
+    return 0;
+}
+
 static SpPerDevice gla_ready;
 
 // mode 0: token by token (any portion); 1: a decode step (needs o_raw)
@@ -659,12 +946,12 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int* 
 
 __global__ void __launch_bounds__(256)
 moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict__ counts, int E, int* __restrict__ sorted,
-                 int* __restrict__ tiles /* [max_tiles][3] */, int max_tiles) {
+                 int* __restrict__ tiles /* [max_tiles][3] */, int max_tiles, int tm) {
     __shared__ int start, tile0, mine, wsum[8], running;
     const int e = blockIdx.x;
     if (threadIdx.x == 0) {
         int s = 0, t0 = 0;
-        for (int x = 0; x < e; ++x) { s += counts[x]; t0 += (counts[x] + ME_TM - 1) / ME_TM; }
+        for (int x = 0; x < e; ++x) { s += counts[x]; t0 += (counts[x] + tm - 1) / tm; }
         start = s; tile0 = t0; mine = counts[e]; running = 0;
     }
     __syncthreads();
@@ -686,25 +973,24 @@ moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict
         }
         __syncthreads();
     }
-    const int n_mine = (mine + ME_TM - 1) / ME_TM;
+    const int n_mine = (mine + tm - 1) / tm;
     for (int i = threadIdx.x; i < n_mine; i += blockDim.x) {
         if (tile0 + i >= max_tiles) break;
         tiles[(tile0 + i) * 3 + 0] = e;
-        tiles[(tile0 + i) * 3 + 1] = start + i * ME_TM;
-        tiles[(tile0 + i) * 3 + 2] = min(ME_TM, mine - i * ME_TM);
+        tiles[(tile0 + i) * 3 + 1] = start + i * tm;
+        tiles[(tile0 + i) * 3 + 2] = min(tm, mine - i * tm);
     }
     if (e == E - 1)
         for (int i = tile0 + n_mine + threadIdx.x; i < max_tiles; i += blockDim.x) tiles[i * 3] = -1;
 }
 
-SP_API int sp_moe_tile_rows() { return ME_TM; }
+SP_API int sp_moe_tile_rows() { return ME_TM; }          // the smallest tile any path uses: sizes the tile table
 
-SP_API int sp_moe_plan(const int* ids, int n_pairs, int E, int* counts, int* sorted, int* tiles, int max_tiles,
-                       cudaStream_t stream) {
-    if (n_pairs <= 0) return 0;
+static int moe_plan(const int* ids, int n_pairs, int E, int* counts, int* sorted, int* tiles, int max_tiles, int tm,
+                    cudaStream_t stream) {
     moe_count_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts);
     SP_CHECK_LAUNCH("moe_count");
-    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles);
+    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, tm);
     SP_CHECK_LAUNCH("moe_place");
     return 0;
 }
@@ -826,6 +1112,96 @@ moe_down_kernel(const TA* __restrict__ act, const TW* __restrict__ wd, const int
     }
 }
 
+// The same products on the tensor cores (bfloat16 operands, 32-bit accumulators): tiles of 64 rows x 64 columns, K in
+// blocks of 32 through two shared-memory stages filled by cp.async; four warps, each 16 rows x all columns with
+// mma.sync m16n8k16 (A and B fragments by ldmatrix from rows padded to 80 bytes). GLU: the tile holds the gate and the
+// up columns of the same outputs and stores the activation; else the result times the pair's weight goes to the
+// pair's row of ``out``. A row's sum runs over k in the same order whatever tile or batch the row is in.
+#define MM_TM 64
+#define MM_BN 64
+#define MM_BK 32
+#define MM_ROW 40
+template <bool GLU>
+__global__ void __launch_bounds__(128)
+moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ Wt, long long w_stride,
+               int N, int K, const int* __restrict__ sorted, const int* __restrict__ tiles, int top,
+               __nv_bfloat16* __restrict__ act, float* __restrict__ out, const float* __restrict__ wts, float limit,
+               float slope) {
+    __shared__ __align__(16) __nv_bfloat16 As[2][MM_TM][MM_ROW];
+    __shared__ __align__(16) __nv_bfloat16 Bs[2][GLU ? 2 : 1][MM_BN][MM_ROW];
+    __shared__ int src_row[MM_TM];
+    const int e = tiles[blockIdx.x * 3];
+    if (e < 0) return;
+    const int first = tiles[blockIdx.x * 3 + 1], rows = tiles[blockIdx.x * 3 + 2];
+    const int n0 = blockIdx.y * MM_BN;
+    if (threadIdx.x < MM_TM)
+        src_row[threadIdx.x] = threadIdx.x < rows ? (GLU ? sorted[first + threadIdx.x] / top : first + threadIdx.x) : -1;
+    __syncthreads();
+    const __nv_bfloat16* w0 = Wt + (size_t)e * w_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nk = (K + MM_BK - 1) / MM_BK;
+
+    auto load = [&](int kb, int st) {
+        for (int c = threadIdx.x; c < MM_TM * 4; c += 128) {
+            const int r = c >> 2, k = kb * MM_BK + (c & 3) * 8;
+            const int src = src_row[r];
+            if (src >= 0 && k < K) cp_async16(smem_u32(&As[st][r][(c & 3) * 8]), A + (size_t)src * lda + k);
+            else *(uint4*)&As[st][r][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
+        }
+        for (int c = threadIdx.x; c < (GLU ? 2 : 1) * MM_BN * 4; c += 128) {
+            const int m = c / (MM_BN * 4), r = (c >> 2) % MM_BN, k = kb * MM_BK + (c & 3) * 8;
+            if (n0 + r < N && k < K) cp_async16(smem_u32(&Bs[st][m][r][(c & 3) * 8]), w0 + ((size_t)m * N + n0 + r) * K + k);
+            else *(uint4*)&Bs[st][m][r][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    };
+
+    float acc[GLU ? 2 : 1][8][4] = {};
+    load(0, 0);
+    for (int kb = 0; kb < nk; ++kb) {
+        if (kb + 1 < nk) {
+            load(kb + 1, (kb + 1) & 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int st = kb & 1;
+#pragma unroll
+        for (int k16 = 0; k16 < MM_BK / 16; ++k16) {
+            uint32_t a[4];
+            ldmatrix_x4(smem_u32(&As[st][warp * 16 + (lane & 15)][k16 * 16 + (lane >> 4) * 8]), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int m = 0; m < (GLU ? 2 : 1); ++m)
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(smem_u32(&Bs[st][m][np * 16 + (lane & 7) + (lane >> 4) * 8][k16 * 16 + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
+                    mma_bf16(acc[m][2 * np], a, b0, b1);
+                    mma_bf16(acc[m][2 * np + 1], a, b2, b3);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int m = warp * 16 + (lane >> 2) + 8 * half;
+        if (m >= rows) continue;
+        const int p = GLU ? 0 : sorted[first + m];
+        const float wt = GLU ? 0.0f : wts[p];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int n = n0 + nt * 8 + (lane & 3) * 2;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (n + u >= N) continue;
+                if (GLU) act[(size_t)(first + m) * N + n + u] = __float2bfloat16_rn(hy_clamped_glu(acc[0][nt][2 * half + u], acc[GLU ? 1 : 0][nt][2 * half + u], limit, slope));
+                else out[(size_t)p * N + n + u] = acc[0][nt][2 * half + u] * wt;
+            }
+        }
+    }
+}
+
 // y[t] += Σ_k out[t·top + k] in the order of k
 __global__ void moe_combine_kernel(const float* __restrict__ out, float* __restrict__ y, size_t T, int top, int W) {
     const size_t n = T * (size_t)W;
@@ -838,11 +1214,28 @@ __global__ void moe_combine_kernel(const float* __restrict__ out, float* __restr
     }
 }
 
-SP_API int sp_moe_experts(const void* x, int x_dt, const void* wgu, const void* wd, int w_dt, const int* sorted,
-                          const int* tiles, int max_tiles, const float* wts, void* act, float* out_pairs, float* y,
-                          int T, int top, int W, int F, float limit, float slope, cudaStream_t stream) {
+SP_API int sp_moe_experts(const void* x, int x_dt, const int* ids, const void* wgu, const void* wd, int w_dt, int E,
+                          int* counts, int* sorted, int* tiles, int max_tiles, const float* wts, void* act, float* out_pairs,
+                          float* y, int T, int top, int W, int F, float limit, float slope, cudaStream_t stream) {
     if (T <= 0) return 0;
-    const dim3 g_up(max_tiles, (F + ME_BN - 1) / ME_BN), g_down(max_tiles, (W + ME_BN - 1) / ME_BN);
+    const int n_pairs = T * top;
+    const bool mma = x_dt == SP_DT_BF16 && w_dt == SP_DT_BF16 && W % 8 == 0 && F % 8 == 0 &&
+                     (((uintptr_t)x | (uintptr_t)wgu | (uintptr_t)wd | (uintptr_t)act) & 15) == 0;
+    const int tm = mma ? MM_TM : ME_TM;
+    if ((n_pairs + tm - 1) / tm + E > max_tiles) SP_FAIL("moe_experts: the tile table is too short");
+    if (moe_plan(ids, n_pairs, E, counts, sorted, tiles, max_tiles, tm, stream)) return 1;
+    if (mma) {
+        const int used = (n_pairs + tm - 1) / tm + E;           // entries beyond the tiles in use say expert -1
+        moe_mma_kernel<true><<<dim3(used, (F + MM_BN - 1) / MM_BN), 128, 0, stream>>>(
+            (const __nv_bfloat16*)x, W, (const __nv_bfloat16*)wgu, 2LL * F * W, F, W, sorted, tiles, top,
+            (__nv_bfloat16*)act, nullptr, nullptr, limit, slope);
+        SP_CHECK_LAUNCH("moe_up (tensor cores)");
+        moe_mma_kernel<false><<<dim3(used, (W + MM_BN - 1) / MM_BN), 128, 0, stream>>>(
+            (const __nv_bfloat16*)act, F, (const __nv_bfloat16*)wd, (long long)W * F, W, F, sorted, tiles, top, nullptr,
+            out_pairs, wts, 0.0f, 0.0f);
+        SP_CHECK_LAUNCH("moe_down (tensor cores)");
+    } else {
+        const dim3 g_up(max_tiles, (F + ME_BN - 1) / ME_BN), g_down(max_tiles, (W + ME_BN - 1) / ME_BN);
 #define ME_LAUNCH(TA, TW)                                                                                             \
     do {                                                                                                              \
         moe_up_kernel<TA, TW><<<g_up, 256, 0, stream>>>((const TA*)x, (const TW*)wgu, sorted, tiles, (TA*)act, top, W, F, limit, slope); \
@@ -850,11 +1243,12 @@ SP_API int sp_moe_experts(const void* x, int x_dt, const void* wgu, const void* 
         moe_down_kernel<TA, TW><<<g_down, 256, 0, stream>>>((const TA*)act, (const TW*)wd, sorted, tiles, wts, out_pairs, W, F); \
         SP_CHECK_LAUNCH("moe_down");                                                                                  \
     } while (0)
-    if (x_dt == SP_DT_F32 && w_dt == SP_DT_F32) ME_LAUNCH(float, float);
-    else if (x_dt == SP_DT_BF16 && w_dt == SP_DT_BF16) ME_LAUNCH(__nv_bfloat16, __nv_bfloat16);
-    else if (x_dt == SP_DT_F32 && w_dt == SP_DT_BF16) ME_LAUNCH(float, __nv_bfloat16);
-    else SP_FAIL("moe_experts: unsupported dtype codes %d/%d", x_dt, w_dt);
+        if (x_dt == SP_DT_F32 && w_dt == SP_DT_F32) ME_LAUNCH(float, float);
+        else if (x_dt == SP_DT_BF16 && w_dt == SP_DT_BF16) ME_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+        else if (x_dt == SP_DT_F32 && w_dt == SP_DT_BF16) ME_LAUNCH(float, __nv_bfloat16);
+        else SP_FAIL("moe_experts: unsupported dtype codes %d/%d", x_dt, w_dt);
 #undef ME_LAUNCH
+    }
     const size_t n = (size_t)T * W;
     const size_t want = (n + 255) / 256;
     moe_combine_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(out_pairs, y, (size_t)T, top, W);

@@ -44,6 +44,8 @@ def load(module: str) -> ctypes.CDLL:
         getattr(lib, f"sp_{module}_last_error").restype = ctypes.c_char_p
         if module == "seqmix":
             lib.sp_retention_chunked_scratch_floats.restype = c_longlong
+        if module == "hybrid":
+            lib.sp_gla_chunked_scratch_floats.restype = c_longlong
         _LIBS[module] = lib
         _LOADED_PATHS[module] = str(path)
         checked = getattr(lib, f"sp_{module}_range_checked", None)
@@ -1064,6 +1066,19 @@ def gla(proj, state, a2, a2_bias, norm_weight, out, step, H, d, vd, rank, tau, e
     _need_contig(proj, state, a2, a2_bias, norm_weight, out)
     o_raw, mode = None, 0
     global launches
+    if not step.all_single and step.max_new >= CHUNKED_FROM and lib.sp_gla_chunked_supported(d, vd, rank):
+        # a prompt: chunks of 64 tokens in parallel (FFMA tiles), their start states by a short scan
+        launches += 4
+        T = proj.shape[0]
+        n_chunks = query_tiles(step.host["new_counts"], int(lib.sp_gla_chunk_tokens()))
+        need = lib.sp_gla_chunked_scratch_floats(n_chunks, T, H, d, vd)
+        scratch = torch.empty(need, dtype=torch.float32, device=proj.device)
+        _check("hybrid", lib.sp_gla_chunked(
+            c_void_p(_ptr(proj)), proj.shape[1], c_void_p(_ptr(state)), state.shape[0], c_void_p(_ptr(a2)),
+            c_void_p(_ptr(a2_bias)), c_void_p(_ptr(norm_weight)), _w_dt(a2, a2_bias, norm_weight), c_void_p(_ptr(scratch)),
+            c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(step.seq_start)), c_void_p(_ptr(step.seq_slot)), step.n_seqs,
+            T, n_chunks, H, d, vd, rank, c_float(tau), c_float(eps), c_float(out_scale), c_void_p(_stream())))
+        return
     if step.all_single and d <= 2048:
         launches += 1                                  # the states streamed once, then the norm and the gate
         o_raw = torch.empty(proj.shape[0] * H * vd, dtype=torch.float32, device=proj.device)
@@ -1127,14 +1142,14 @@ def moe_experts(x, ids, weights, w_gate_up, w_down, y, top, limit, slope=1.702):
     dev = x.device
     book = torch.empty(E + n_pairs + 3 * max_tiles, dtype=torch.int32, device=dev)
     counts, order, tiles = book[:E], book[E:E + n_pairs], book[E + n_pairs:]
+    if ids.dtype != torch.int32 or weights.dtype != torch.float32 or y.dtype != torch.float32:
+        raise KernelError("moe_experts takes int32 ids, float32 weights and adds into a float32 matrix")
     act = torch.empty(n_pairs, F, dtype=x.dtype, device=dev)
     out_pairs = torch.empty(n_pairs, W, dtype=torch.float32, device=dev)
     global launches
     launches += 4
-    _check("hybrid", lib.sp_moe_plan(c_void_p(_ptr(ids)), n_pairs, E, c_void_p(_ptr(counts)), c_void_p(_ptr(order)),
-                                     c_void_p(_ptr(tiles)), max_tiles, c_void_p(_stream())))
     _check("hybrid", lib.sp_moe_experts(
-        c_void_p(_ptr(x)), dt_code(x), c_void_p(_ptr(w_gate_up)), c_void_p(_ptr(w_down)), _w_dt(w_gate_up, w_down),
-        c_void_p(_ptr(order)), c_void_p(_ptr(tiles)), max_tiles, c_void_p(_ptr(weights)), c_void_p(_ptr(act)),
-        c_void_p(_ptr(out_pairs)), c_void_p(_ptr(y)), T, int(top), W, F, c_float(limit), c_float(slope),
-        c_void_p(_stream())))
+        c_void_p(_ptr(x)), dt_code(x), c_void_p(_ptr(ids)), c_void_p(_ptr(w_gate_up)), c_void_p(_ptr(w_down)),
+        _w_dt(w_gate_up, w_down), E, c_void_p(_ptr(counts)), c_void_p(_ptr(order)), c_void_p(_ptr(tiles)), max_tiles,
+        c_void_p(_ptr(weights)), c_void_p(_ptr(act)), c_void_p(_ptr(out_pairs)), c_void_p(_ptr(y)), T, int(top), W, F,
+        c_float(limit), c_float(slope), c_void_p(_stream())))

@@ -240,7 +240,7 @@ def test_gated_linear_attention_whole_in_portions_and_token_by_token(H, d, vd, r
     from spissa_b200.csrc import lib as K
     g = torch.Generator().manual_seed(H * d + vd)
     W, eps, scale = 24, 1e-4, 0.6
-    lengths, slots = [37, 5], [1, 3]
+    lengths, slots = [150, 37], [1, 3]
     w = {"q": torch.randn(H * d, W, generator=g) * 0.3, "k": torch.randn(H * d, W, generator=g) * 0.3,
          "v": torch.randn(H * vd, W, generator=g) * 0.3, "g": torch.randn(H * vd, W, generator=g) * 0.3,
          "a1": torch.randn(rank, W, generator=g), "a2": torch.randn(H * d, rank, generator=g),
@@ -271,7 +271,9 @@ def test_gated_linear_attention_whole_in_portions_and_token_by_token(H, d, vd, r
         assert float((state[0] - 7.0).abs().max()) == 0.0
         return [torch.cat(r) for r in rows]
 
-    for cuts in ([[37], [5]], [[2, 33, 1, 1], [1, 1, 1, 2]], [[1] * 37, [1] * 5 + [0] * 32], [[16, 16, 5], [0, 5, 0]]):
+    # whole (chunks of 64 with a ragged last one), portions that start chunks elsewhere, short portions, token by token
+    for cuts in ([[150], [37]], [[64, 86], [0, 37]], [[2, 33, 114, 1], [1, 1, 33, 2]], [[1] * 150, [1] * 37 + [0] * 113],
+                 [[100, 16, 34], [5, 32, 0]]):
         got = run(cuts)
         for b in range(2):
             assert worst(got[b], refs[b]) <= 2e-5, (cuts, b)
@@ -311,6 +313,35 @@ def test_router_choice_and_experts(E, top, groups, keep):
     y0 = torch.zeros(T, W, device=DEV)
     K.moe_experts(x.to(DEV), ids, wts, gu, dn, y0, top, limit)
     assert torch.equal(y1[0], y0[5])
+
+
+@pytest.mark.parametrize("T,W,F,E,top", [(150, 72, 40, 8, 2), (3, 64, 136, 16, 4), (700, 200, 64, 4, 3)])
+def test_experts_on_the_tensor_cores(T, W, F, E, top):
+    """bfloat16 rows and weights whose sizes are multiples of eight take the tensor-core tiles: the result is the
+    plain one on the same rounded operands, up to the rounding of the activation; a token's row does not depend on
+    the batch it is in."""
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(T + W)
+    limit = 1.3
+    x = torch.randn(T, W, generator=g).bfloat16()
+    w = {"router": torch.randn(E, W, generator=g) * 0.5, "correction": torch.zeros(E)}
+    for e in range(E):
+        for n, shape in (("gate", (F, W)), ("up", (F, W)), ("down", (W, F))):
+            w[f"e{e}.{n}"] = (torch.randn(shape, generator=g) * 0.3).bfloat16()
+    wd = {k: v.double() for k, v in w.items()}
+    r = dict(experts=E, top=top)
+    idx, wt = G.route(x.double(), wd, "", r)
+    ref = G.moe_ff(x.double(), wd, "", dict(router=r, expert=dict(limit=limit)))
+    gu = torch.stack([torch.cat([w[f"e{e}.gate"], w[f"e{e}.up"]]) for e in range(E)]).to(DEV)
+    dn = torch.stack([w[f"e{e}.down"] for e in range(E)]).to(DEV)
+    ids, wts = idx.int().to(DEV).contiguous(), wt.float().to(DEV).contiguous()
+    y = torch.zeros(T, W, device=DEV)
+    K.moe_experts(x.to(DEV), ids, wts, gu, dn, y, top, limit)
+    assert worst(y, ref) <= 8e-3
+    t = T // 2
+    y1 = torch.zeros(1, W, device=DEV)
+    K.moe_experts(x[t:t + 1].to(DEV), ids[t:t + 1].contiguous(), wts[t:t + 1].contiguous(), gu, dn, y1, top, limit)
+    assert torch.equal(y1[0], y[t])
 
 
 def test_activations_and_attention_with_values_of_another_size():
