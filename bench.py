@@ -296,10 +296,12 @@ def design_compare(args) -> int:
             engine.phase_totals.clear()
             for sl in slots:
                 engine.release(sl)
-            s = engine.acquire()
-            engine.step([(s, prompt, [T - 1])])
-            pre_phases = dict(engine.phase_totals["prefill"]["ms"])
-            engine.release(s)
+            for _ in range(2):                                    # the second run's: the first also pays for fresh scratch
+                engine.phase_totals.clear()
+                s = engine.acquire()
+                engine.step([(s, prompt, [T - 1])])
+                pre_phases = dict(engine.phase_totals["prefill"]["ms"])
+                engine.release(s)
             slots = [engine.acquire() for _ in range(B)]
             engine.step([(sl, prompt[:T - 8], []) for sl in slots])
             engine.phase_totals.pop("decode", None)
@@ -396,7 +398,7 @@ def gozatar_rooflines(size, goz, row, T, peaks, eb) -> dict:
                             frac=frac(L * T * ((2 * rh * rd + 2 * rh * rvd + 16) * 4.0 + rh * rvd * eb), bw, gz.get("gla_ms")))
     # the experts: 4 of 32 per token, three matrices of W x ff/4 each
     out["experts (tensor)"] = dict(ms=gz.get("experts_ms"), frac=frac(n_moe * T * 4 * 3 * 2.0 * W * (ff // 4), tf, gz.get("experts_ms")))
-    ll_ff = (ll.get("gate_projection+up_projection+activation_multiply_ms") or 0) + (ll.get("down_projection+mlp_residual_ms") or 0)
+    ll_ff = sum(v for k, v in ll.items() if "gate_projection" in k or "down_projection" in k)
     out["llama feed-forward (tensor)"] = dict(ms=ll_ff, frac=frac(ll_runs * T * 3 * 2.0 * W * ff, tf, ll_ff))
     C = (h + g) * d + g * d
     out["conv+rotary+store (hbm)"] = dict(ms=gz.get("conv+rotary+kv_append_ms"),

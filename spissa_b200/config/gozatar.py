@@ -73,9 +73,7 @@ class GozatarConfig:
                 raise ConfigError(f"{lw}heads {heads} must be a multiple of kv_heads {kvh}")
             dim = _positive(l, "dim", lw)
             left = dict(heads=heads, kv_heads=kvh, dim=dim, vdim=_positive(l, "vdim", lw, optional=True) or dim,
-                        conv=_get(l, "conv", lw, optional=True) or 1, scale=float(_get(l, "scale", lw, _NUM)))
-            if left["conv"] < 1:
-                raise ConfigError(f"{lw}conv must be at least 1")
+                        conv=_positive(l, "conv", lw, optional=True), scale=float(_get(l, "scale", lw, _NUM)))
             mask = _get(l, "mask", lw, (dict,), optional=True)
             left["window"] = _positive(mask, "size", lw + "mask.") if mask else None
             rot = _get(l, "rot", lw, (dict,), optional=True)
@@ -91,6 +89,7 @@ class GozatarConfig:
                 raise ConfigError(f"{rw}tau must be positive")
             mixer = dict(left=left, right=right, left_scale=float(_get(m, "left_scale", where + "mixer.", _NUM)),
                          right_scale=float(_get(m, "right_scale", where + "mixer.", _NUM)))
+            # "conv" absent: no convolution and no such tensors; present, even as 1: that many taps
             mlp = layer.get("mlp")
             if mlp is not None:
                 mw = where + "mlp."
@@ -126,8 +125,8 @@ class GozatarConfig:
             return dict(self.raw)
         layers = []
         for l in self.layers:
-            left = dict(l["mixer"]["left"])
-            w, rd, rb = left.pop("window"), left.pop("rot_dims"), left.pop("rot_base")
+            left = {k: v for k, v in l["mixer"]["left"].items() if v is not None}
+            w, rd, rb = left.pop("window", None), left.pop("rot_dims"), left.pop("rot_base")
             if w:
                 left["mask"] = dict(size=w)
             if rd:

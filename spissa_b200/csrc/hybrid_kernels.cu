@@ -41,12 +41,14 @@ struct HcArgs {
     float eps;
 };
 
-__global__ void streams_norm_kernel(HcArgs a) {
-    extern __shared__ float u[];                       // [W] the norm's input
-    __shared__ float red[32];
+// One warp per token row (no block-wide waits); a lane takes groups of VEC neighbouring columns (VEC 4: 16-byte loads
+// and stores, for widths that are multiples of four). The norm's input waits in shared memory between the passes
+// (mean, then the mean of the squared deviations, then the store); each lane reads back only what it wrote.
+#define SN_WARPS 4
+template <int VEC>
+__global__ void __launch_bounds__(SN_WARPS * 32) streams_norm_kernel(HcArgs a) {
+    extern __shared__ __align__(16) float u_all[];     // [SN_WARPS][W rounded up to 4]
     __shared__ float cm[HC_MAX_STREAMS * HC_MAX_STREAMS], co[HC_MAX_STREAMS], ci[HC_MAX_STREAMS];
-    const int r = blockIdx.x;
-    if (r >= a.n_rows) return;
     const int S = a.S, W = a.W;
     if (threadIdx.x < S * S) cm[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.0f : 0.0f);
     if (threadIdx.x < S) {
@@ -54,50 +56,93 @@ __global__ void streams_norm_kernel(HcArgs a) {
         ci[threadIdx.x] = a.inc ? a.inc[threadIdx.x] : 1.0f;
     }
     __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * SN_WARPS + warp;
+    if (r >= a.n_rows) return;
+    float* u = u_all + (size_t)warp * ((W + 3) / 4 * 4);
     const size_t row = a.rows ? (size_t)a.rows[r] : (size_t)r;
     float* xr = a.x + row * S * W;
     float part = 0.0f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float xs[HC_MAX_STREAMS];
+    for (int c = lane * VEC; c < W; c += 32 * VEC) {
+        float xs[HC_MAX_STREAMS][VEC];
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * W + c] : 0.0f;
+        for (int s = 0; s < HC_MAX_STREAMS; ++s) {
+            if (s >= S) break;
+            if (VEC == 4) {
+                const float4 v = *(const float4*)(xr + (size_t)s * W + c);
+                xs[s][0] = v.x; xs[s][1] = v.y; xs[s][2] = v.z; xs[s][VEC - 1] = v.w;
+            } else {
+                xs[s][0] = xr[(size_t)s * W + c];
+            }
+        }
         if (a.y) {
-            const float yv = a.y[row * W + c];
-            a.y[row * W + c] = 0.0f;
-            float nx[HC_MAX_STREAMS];
+            float yv[VEC];
+            if (VEC == 4) {
+                const float4 v = *(const float4*)(a.y + row * W + c);
+                yv[0] = v.x; yv[1] = v.y; yv[2] = v.z; yv[VEC - 1] = v.w;
+                *(float4*)(a.y + row * W + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            } else {
+                yv[0] = a.y[row * W + c];
+                a.y[row * W + c] = 0.0f;
+            }
+            float nx[HC_MAX_STREAMS][VEC];
 #pragma unroll
             for (int t = 0; t < HC_MAX_STREAMS; ++t) {
                 if (t >= S) break;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    float v = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                        if (s < S) v = fmaf(cm[s * S + t], xs[s][i], v);
+                    nx[t][i] = fmaf(co[t], yv[i], v);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+                if (t >= S) break;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) xs[t][i] = nx[t][i];
+                if (VEC == 4) *(float4*)(xr + (size_t)t * W + c) = make_float4(nx[t][0], nx[t][1], nx[t][2], nx[t][VEC - 1]);
+                else xr[(size_t)t * W + c] = nx[t][0];
+            }
+        }
+        if (a.w) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
                 float v = 0.0f;
 #pragma unroll
                 for (int s = 0; s < HC_MAX_STREAMS; ++s)
-                    if (s < S) v = fmaf(cm[s * S + t], xs[s], v);
-                nx[t] = fmaf(co[t], yv, v);
+                    if (s < S) v = fmaf(ci[s], xs[s][i], v);
+                u[c + i] = v;
+                part += v;
             }
-#pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t)
-                if (t < S) { xs[t] = nx[t]; xr[(size_t)t * W + c] = nx[t]; }
-        }
-        if (a.w) {
-            float v = 0.0f;
-#pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s)
-                if (s < S) v = fmaf(ci[s], xs[s], v);
-            u[c] = v;
-            part += v;
         }
     }
     if (!a.w) return;
-    const float mean = sp_block_sum(part, red) / (float)W;
+    const float mean = sp_warp_sum(part) / (float)W;
     float dev = 0.0f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float dlt = u[c] - mean;
-        dev = fmaf(dlt, dlt, dev);
-    }
-    const float var = sp_block_sum(dev, red) / (float)W;
+    for (int c = lane * VEC; c < W; c += 32 * VEC)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const float dlt = u[c + i] - mean;
+            dev = fmaf(dlt, dlt, dev);
+        }
+    const float var = sp_warp_sum(dev) / (float)W;
     const float inv = 1.0f / sqrtf(var + a.eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x)
-        sp_st_dt(a.out, a.out_dt, (size_t)r * W + c, (u[c] - mean) * inv * sp_ld_dt(a.w, a.w_dt, c));
+    for (int c = lane * VEC; c < W; c += 32 * VEC) {
+        float o[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = (u[c + i] - mean) * inv * sp_ld_dt(a.w, a.w_dt, c + i);
+        if (VEC == 4 && a.out_dt == SP_DT_F32) {
+            *(float4*)((float*)a.out + (size_t)r * W + c) = make_float4(o[0], o[1], o[2], o[VEC - 1]);
+        } else if (VEC == 4) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[VEC - 1]);
+            *(uint2*)((__nv_bfloat16*)a.out + (size_t)r * W + c) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        } else {
+            sp_st_dt(a.out, a.out_dt, (size_t)r * W + c, o[0]);
+        }
+    }
 }
 
 static SpPerDevice streams_norm_ready;
@@ -108,15 +153,19 @@ SP_API int sp_streams_norm(float* x, float* y, const float* mix, const float* ou
     if (n_rows <= 0) return 0;
     if (S < 1 || S > HC_MAX_STREAMS) SP_FAIL("streams_norm: %d streams, this kernel takes 1 to %d", S, HC_MAX_STREAMS);
     if (y && rows) SP_FAIL("streams_norm: an update runs over all rows");
-    const size_t smem = (size_t)W * sizeof(float);
+    const size_t smem = (size_t)SN_WARPS * ((W + 3) / 4 * 4) * sizeof(float);
     if (smem > 200 * 1024) SP_FAIL("streams_norm: a row of %d does not fit shared memory", W);
     if (smem > 48 * 1024 && !streams_norm_ready.done()) {
-        if (cudaFuncSetAttribute(streams_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(streams_norm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(streams_norm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
             SP_FAIL("streams_norm: cannot raise the shared memory limit");
         streams_norm_ready.mark();
     }
     HcArgs a{x, y, mix, outc, inc, w, w_dt, out, out_dt, rows, n_rows, S, W, eps};
-    streams_norm_kernel<<<n_rows, W >= 1024 ? 256 : 128, smem, stream>>>(a);
+    const bool wide = W % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)out)) & 15) == 0;
+    const int blocks = (n_rows + SN_WARPS - 1) / SN_WARPS;
+    if (wide) streams_norm_kernel<4><<<blocks, SN_WARPS * 32, smem, stream>>>(a);
+    else streams_norm_kernel<1><<<blocks, SN_WARPS * 32, smem, stream>>>(a);
     SP_CHECK_LAUNCH("streams_norm");
     return 0;
 }
@@ -549,10 +598,35 @@ __global__ void __launch_bounds__(256) gla_chunk_prep_kernel(GlcArgs c) {
         }
     }
     __syncthreads();
+    // How far the chunk's decays go: where e^{−B} stays far inside the 32-bit range (the usual case), P is the plain
+    // product of q ⊙ e^{B} and k ⊙ e^{−B} (two exponentials per token and channel); else every pair takes its own
+    // e^{B_i − B_j} ≤ 1, which cannot overflow whatever the decays are.
+    __shared__ float red[32];
+    float far = 0.0f;
+    for (int e = threadIdx.x; e < d; e += blockDim.x) far = fmaxf(far, -bT[e * GLC_TS + GLC - 1]);
+    far = sp_block_max(far, red);
+    const bool plain = far <= 60.0f;
     // P: thread (ty, tx) owns pairs i = 4ty … 4ty+3, j = 4tx … 4tx+3; blocks above the diagonal stay zero
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     float p[4][4] = {};
-    if (tx <= ty) {
+    if (plain) {
+        __syncthreads();
+        for (int x = threadIdx.x; x < GLC * d; x += blockDim.x) {
+            const int e = x / GLC, i = x % GLC;
+            const float b = bT[e * GLC_TS + i];
+            qT[e * GLC_TS + i] *= expf(b);
+            kT[e * GLC_TS + i] *= expf(-b);
+        }
+        __syncthreads();
+        if (tx <= ty) {
+            glc_mm<1>(qT, GLC_TS, kT, GLC_TS, d, p, ty, tx);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    if (4 * tx + v > 4 * ty + u) p[u][v] = 0.0f;
+        }
+    } else if (tx <= ty) {
         for (int e = 0; e < d; ++e) {
             const float4 q4 = *(const float4*)(qT + e * GLC_TS + 4 * ty), bi4 = *(const float4*)(bT + e * GLC_TS + 4 * ty);
             const float4 k4 = *(const float4*)(kT + e * GLC_TS + 4 * tx), bj4 = *(const float4*)(bT + e * GLC_TS + 4 * tx);
@@ -573,8 +647,9 @@ __global__ void __launch_bounds__(256) gla_chunk_prep_kernel(GlcArgs c) {
     for (int x = threadIdx.x; x < n * d; x += blockDim.x) {
         const int i = x / d, e = x % d;
         const float b = bT[e * GLC_TS + i], bl = bT[e * GLC_TS + GLC - 1];
-        c.qe[(size_t)(t0 + i) * Hd + h * d + e] = qT[e * GLC_TS + i] * expf(b);
-        c.ke[(size_t)(t0 + i) * Hd + h * d + e] = kT[e * GLC_TS + i] * expf(bl - b);
+        const float qv = qT[e * GLC_TS + i], kv = kT[e * GLC_TS + i];
+        c.qe[(size_t)(t0 + i) * Hd + h * d + e] = plain ? qv : qv * expf(b);
+        c.ke[(size_t)(t0 + i) * Hd + h * d + e] = plain ? kv * expf(bl) : kv * expf(bl - b);
     }
     for (int e = threadIdx.x; e < d; e += blockDim.x) c.dl[((size_t)blockIdx.x * a.H + h) * d + e] = expf(bT[e * GLC_TS + GLC - 1]);
 }
@@ -630,7 +705,8 @@ __global__ void __launch_bounds__(256) gla_chunk_scan_kernel(GlcArgs c) {
     float* st = a.state + ((size_t)slot * a.H + h) * a.d * a.vd + x;
     float S = *st;
     const int e = x / a.vd;
-    for (int k = 0; k < nc; ++k) {
+#pragma unroll 8
+    for (int k = 0; k < nc; ++k) {                   // the loads do not depend on S: several chunks' are in flight
         float* slot_k = c.cs + ((size_t)(first_chunk + k) * a.H + h) * a.d * a.vd + x;
         const float own = *slot_k;
         *slot_k = S;
@@ -1112,12 +1188,13 @@ moe_down_kernel(const TA* __restrict__ act, const TW* __restrict__ wd, const int
     }
 }
 
-// The same products on the tensor cores (bfloat16 operands, 32-bit accumulators): tiles of 64 rows x 64 columns, K in
-// blocks of 32 through two shared-memory stages filled by cp.async; four warps, each 16 rows x all columns with
-// mma.sync m16n8k16 (A and B fragments by ldmatrix from rows padded to 80 bytes). GLU: the tile holds the gate and the
+// The same products on the tensor cores (bfloat16 operands, 32-bit accumulators): tiles of 128 rows x 64 columns, K in
+// blocks of 32 through two shared-memory stages filled by cp.async; four warps, each 32 rows x all columns with
+// mma.sync m16n8k16 (A and B fragments by ldmatrix from rows padded to 80 bytes); a group of 16 rows beyond the tile's
+// rows (a decode step's tiles hold a row or two) is skipped. GLU: the tile holds the gate and the
 // up columns of the same outputs and stores the activation; else the result times the pair's weight goes to the
 // pair's row of ``out``. A row's sum runs over k in the same order whatever tile or batch the row is in.
-#define MM_TM 64
+#define MM_TM 128
 #define MM_BN 64
 #define MM_BK 32
 #define MM_ROW 40
@@ -1156,7 +1233,8 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
         cp_async_commit();
     };
 
-    float acc[GLU ? 2 : 1][8][4] = {};
+    float acc[2][GLU ? 2 : 1][8][4] = {};
+    const bool live[2] = {warp * 32 < rows, warp * 32 + 16 < rows};
     load(0, 0);
     for (int kb = 0; kb < nk; ++kb) {
         if (kb + 1 < nk) {
@@ -1167,39 +1245,50 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
         }
         __syncthreads();
         const int st = kb & 1;
+        if (live[0]) {
 #pragma unroll
-        for (int k16 = 0; k16 < MM_BK / 16; ++k16) {
-            uint32_t a[4];
-            ldmatrix_x4(smem_u32(&As[st][warp * 16 + (lane & 15)][k16 * 16 + (lane >> 4) * 8]), a[0], a[1], a[2], a[3]);
+            for (int k16 = 0; k16 < MM_BK / 16; ++k16) {
+                uint32_t a[2][4];
 #pragma unroll
-            for (int m = 0; m < (GLU ? 2 : 1); ++m)
+                for (int f = 0; f < 2; ++f)
+                    if (f == 0 || live[1])
+                        ldmatrix_x4(smem_u32(&As[st][warp * 32 + f * 16 + (lane & 15)][k16 * 16 + (lane >> 4) * 8]), a[f][0], a[f][1], a[f][2], a[f][3]);
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(smem_u32(&Bs[st][m][np * 16 + (lane & 7) + (lane >> 4) * 8][k16 * 16 + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
-                    mma_bf16(acc[m][2 * np], a, b0, b1);
-                    mma_bf16(acc[m][2 * np + 1], a, b2, b3);
-                }
+                for (int m = 0; m < (GLU ? 2 : 1); ++m)
+#pragma unroll
+                    for (int np = 0; np < 4; ++np) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(smem_u32(&Bs[st][m][np * 16 + (lane & 7) + (lane >> 4) * 8][k16 * 16 + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
+                        mma_bf16(acc[0][m][2 * np], a[0], b0, b1);
+                        mma_bf16(acc[0][m][2 * np + 1], a[0], b2, b3);
+                        if (live[1]) {
+                            mma_bf16(acc[1][m][2 * np], a[1], b0, b1);
+                            mma_bf16(acc[1][m][2 * np + 1], a[1], b2, b3);
+                        }
+                    }
+            }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int m = warp * 16 + (lane >> 2) + 8 * half;
-        if (m >= rows) continue;
-        const int p = GLU ? 0 : sorted[first + m];
-        const float wt = GLU ? 0.0f : wts[p];
+    for (int f = 0; f < 2; ++f)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            const int n = n0 + nt * 8 + (lane & 3) * 2;
+        for (int half = 0; half < 2; ++half) {
+            const int m = warp * 32 + f * 16 + (lane >> 2) + 8 * half;
+            if (m >= rows) continue;
+            const int p = GLU ? 0 : sorted[first + m];
+            const float wt = GLU ? 0.0f : wts[p];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (n + u >= N) continue;
-                if (GLU) act[(size_t)(first + m) * N + n + u] = __float2bfloat16_rn(hy_clamped_glu(acc[0][nt][2 * half + u], acc[GLU ? 1 : 0][nt][2 * half + u], limit, slope));
-                else out[(size_t)p * N + n + u] = acc[0][nt][2 * half + u] * wt;
+            for (int nt = 0; nt < 8; ++nt) {
+                const int n = n0 + nt * 8 + (lane & 3) * 2;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (n + u >= N) continue;
+                    if (GLU) act[(size_t)(first + m) * N + n + u] = __float2bfloat16_rn(hy_clamped_glu(acc[f][0][nt][2 * half + u], acc[f][GLU ? 1 : 0][nt][2 * half + u], limit, slope));
+                    else out[(size_t)p * N + n + u] = acc[f][0][nt][2 * half + u] * wt;
+                }
             }
         }
-    }
 }
 
 // y[t] += Σ_k out[t·top + k] in the order of k

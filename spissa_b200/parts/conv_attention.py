@@ -33,7 +33,7 @@ class ConvAttention(GQAAttention):
     kernel_modules_bf16 = ("attention",)
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int | None = None,
-                 conv_taps: int = 1, scale: float | None = None, qk_norm_eps: float | None = None,
+                 conv_taps: int | None = None, scale: float | None = None, qk_norm_eps: float | None = None,
                  out_scale: float = 1.0, position=None, window=None, prefix: str = "", names: dict | None = None):
         n = dict(q="q", k="k", v="v", o="o", conv_suffix=".conv")
         n.update(names or {})
@@ -41,7 +41,7 @@ class ConvAttention(GQAAttention):
         super().__init__(hidden_size, num_heads, num_kv_heads, head_dim, position=position, window=window,
                          prefix=prefix, names=n)
         self.v_head_dim = int(v_head_dim or head_dim)
-        self.conv_taps = max(1, int(conv_taps or 1))
+        self.conv_taps = int(conv_taps or 0)       # 0: no convolution and no tensors for one; 1: a weight per channel
         if scale is not None:
             self.scale = float(scale)
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
@@ -56,7 +56,7 @@ class ConvAttention(GQAAttention):
         H, nh, nkv, d, vd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
         shapes = dict(q=(nh * d, H), k=(nkv * d, H), v=(nkv * vd, H))
         specs = [WeightSpec(self.names[k], s) for k, s in shapes.items()] + [WeightSpec(self.names["o"], (H, nh * vd))]
-        if self.conv_taps > 1:
+        if self.conv_taps >= 1:
             specs += [WeightSpec(self.names[k] + self.conv_suffix, (s[0], self.conv_taps), init="const:0.5")
                       for k, s in shapes.items()]
         return specs
@@ -71,7 +71,7 @@ class ConvAttention(GQAAttention):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        if self.conv_taps > 1:
+        if self.conv_taps >= 1:
             self.conv = torch.cat([tensors[self.names[k] + self.conv_suffix] for k in ("q", "k", "v")], dim=0).contiguous()
 
     def forward(self, x, step, cache, residual):
@@ -85,7 +85,7 @@ class ConvAttention(GQAAttention):
             qkv = self.qkv(x, out_dtype=torch.float32)             # convolution and rotation read unrounded products
         with phase("conv+rotary+kv_append_ms"):
             q = torch.empty(x.shape[0], nh * d, dtype=self.rt.act_dtype, device=x.device)
-            K.conv_qk_store(qkv, self.conv, self.conv_taps, state, q, kv.k_pool, kv.v_pool, kv, step, inv_freq, nh, nkv,
+            K.conv_qk_store(qkv, self.conv, max(1, self.conv_taps), state, q, kv.k_pool, kv.v_pool, kv, step, inv_freq, nh, nkv,
                             d, vd, rd, self.qk_norm_eps or 0.0, v_scale=self.out_scale,
                             unit_rms=self.qk_norm_eps is not None)
         with phase("attention_ms"):

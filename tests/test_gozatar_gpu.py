@@ -66,7 +66,7 @@ def model(width, vocab, layers, mlps, streams=None, eps=1e-5):
 
 
 # sizes that differ from one another everywhere: grouped, multi-head and single-kv-head attention; key and value sizes
-# equal or not; convolutions of 4, 2, 3 taps or none; rotation over a part of the dims, all, or none; windows below and
+# equal or not; convolutions of 4, 2, 3, 5 taps, of one tap (a weight per channel) or none; rotation over a part of the dims, all, or none; windows below and
 # above a page, or none; one, three, four streams or plain residual sums; experts in groups of 2, 3, 1 or ungrouped,
 # with and without a shared expert; layers without a feed-forward
 CONFIGS = {
@@ -75,7 +75,7 @@ CONFIGS = {
                          par(left(2, 2, 16, 48, conv=3, rot=4, window=70), 1, 8, 24, 2.0, 0.5, 1.5)],
                [moe(8, 2, 24, 1.5, groups=(4, 2), shared=(40, 3.0)), dense(80), None], streams=3),
     "b": model(96, 333, [par(left(3, 3, 12, 20, conv=2, rot=12, window=70), 1, 16, 40, 1.0, 1.0, 1.0),
-                         par(left(6, 2, 16, 16, rot=6, base=500.0, window=130), 2, 8, 8, 8.0, 0.3, 0.6)],
+                         par(left(6, 2, 16, 16, conv=1, rot=6, base=500.0, window=130), 2, 8, 8, 8.0, 0.3, 0.6)],
                [moe(6, 3, 32, 0.8), moe(9, 3, 16, 2.5, groups=(3, 1), shared=(24, 1.0))], streams=1, eps=1e-3),
     "c": model(48, 150, [par(left(2, 1, 32, 32), 3, 8, 8, 30.0, 0.9, 0.2),
                          par(left(1, 1, 16, 8, conv=3, window=33), 2, 4, 12, 0.7, 1.0, 1.0)],
