@@ -711,6 +711,64 @@ def kernel_case(name: str, reps: int) -> int:
             out = torch.empty(T, Wd, dtype=bf, device=dev)
             run = lambda i: K.token_shift(xs[i % 6], mu, state, out, step, dyt=(w, b, al))
             bytes_ = T * Wd * (4 + 2.0)
+    elif name in ("gla_chunks", "gla_step", "moe_experts", "moe_experts_b8", "streams_norm", "conv_qk_store"):
+        # the Gozatar kernels at the 2k size of --design (8 heads of 128 x 256, width 2,048, 32 experts of 2,048, 4 per token)
+        rh, rd, rvd, Wd, rank = 8, 128, 256, 2048, 16
+        B = 8 if name in ("gla_step", "moe_experts_b8") else 1
+        n_new = 1 if B > 1 else T
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        step = SimpleNamespace(seq_start=i32([n_new * b for b in range(B + 1)]), seq_slot=i32(list(range(B))),
+                               token_seq=torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(n_new), n_seqs=B,
+                               positions=torch.arange(n_new, dtype=torch.int32, device=dev).repeat(B),
+                               all_single=n_new == 1, max_new=n_new, host=dict(new_counts=[n_new] * B))
+        if name.startswith("gla"):
+            n_buf = 6 if B > 1 else 1
+            proj = torch.randn(B * n_new, 2 * rh * rd + 2 * rh * rvd + rank, device=dev)
+            states = [torch.zeros(B, rh, rd, rvd, device=dev) for _ in range(n_buf)]
+            a2, a2b, nw = rnd(rh * rd, rank), rnd(rh * rd), rnd(rvd)
+            out = torch.empty(B * n_new, rh * rvd, dtype=bf, device=dev)
+            run = lambda i: K.gla(proj, states[i % n_buf], a2, a2b, nw, out, step, rh, rd, rvd, rank, 16.0, 1e-6, 0.7)
+            if B > 1:
+                bytes_ = B * rh * rd * rvd * 4 * 2.0
+            else:
+                flops = T * rh * 4.0 * rd * rvd              # the recurrence's own FLOPs (the chunked form does several times as many)
+        elif name.startswith("moe_experts"):
+            E, top, F = 32, 4, 2048
+            rows = B * n_new
+            n_buf = 4 if B > 1 else 1                        # a decode step streams the experts it touches: rotate them
+            gus = [rnd(E, 2 * F, Wd) for _ in range(n_buf)]
+            dns = [rnd(E, Wd, F) for _ in range(n_buf)]
+            x = rnd(rows, Wd)
+            ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).int().contiguous()
+            wts = torch.full((rows, top), 1.0 / top, device=dev)
+            y = torch.zeros(rows, Wd, device=dev)
+            run = lambda i: K.moe_experts(x, ids, wts, gus[i % n_buf], dns[i % n_buf], y, top, 7.0)
+            if B > 1:
+                bytes_ = len(set(ids.flatten().tolist())) * 3.0 * F * Wd * 2
+            else:
+                flops = rows * top * 3 * 2.0 * Wd * F
+        elif name == "streams_norm":
+            S = 2
+            xs = [torch.randn(T, S * Wd, device=dev) for _ in range(4)]
+            ys = [torch.randn(T, Wd, device=dev) for _ in range(4)]
+            mix, oc, ic, w = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.ones(S, device=dev) / S, rnd(Wd)
+            out = torch.empty(T, Wd, dtype=bf, device=dev)
+            run = lambda i: K.streams_norm(xs[i % 4], S, Wd, out=out, weight=w, eps=1e-6, y=ys[i % 4], mix=mix, out_coef=oc, in_coef=ic)
+            bytes_ = T * Wd * (2 * S * 4 + 2 * 4 + 2.0)
+        else:
+            nh, nkv, d = 16, 4, 128
+            C = (nh + 2 * nkv) * d
+            qkvs = [torch.randn(T, C, device=dev) for _ in range(4)]
+            conv = rnd(C, 4)
+            state = torch.zeros(1, 3, C, device=dev)
+            inv_freq = (10000.0 ** (-torch.arange(0, d // 2, 2, device=dev).float() / (d // 2))).contiguous()
+            q = torch.empty(T, nh * d, dtype=bf, device=dev)
+            pages = T // 64
+            kp, vp = rnd(pages, nkv, 64, d), rnd(pages, nkv, 64, d)
+            meta = SimpleNamespace(page_table=torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages), page_size=64,
+                                   seq_slot=i32([0]), positions=step.positions, token_seq=step.token_seq)
+            run = lambda i: K.conv_qk_store(qkvs[i % 4], conv, 4, state, q, kp, vp, meta, step, inv_freq, nh, nkv, d, d, d // 2, 1e-6)
+            bytes_ = T * C * (4 + 2.0)
     elif name in ("sample_b8", "sample_b64", "argmax_b8"):
         # the sampler on rows of 128,256 logits (standard deviation 4 after the temperature): temperature 0.8, top-p 0.95
         B = 64 if name.endswith("b64") else 8
@@ -772,7 +830,7 @@ def main() -> int:
                     help="add per-phase timings of one prompt step and of part-by-part decode steps")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|diff_flash|diff_decode|retention_chunks|retention_step|mingru_chunks|polynorm|token_shift|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
+                         "gemv_down|gemv_head|diff_flash|diff_decode|retention_chunks|retention_step|mingru_chunks|polynorm|token_shift|gla_chunks|gla_step|moe_experts|moe_experts_b8|streams_norm|conv_qk_store|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
     ap.add_argument("--design", default=None, choices=["duzinex", "gozatar"],
                     help="measure this design beside the Llama decoder at equal layer sizes instead of the headline workload")
     ap.add_argument("--design-sizes", default="", dest="design_sizes", help="which of 1k,2k,4k (default: all)")

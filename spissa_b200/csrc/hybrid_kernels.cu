@@ -41,32 +41,30 @@ struct HcArgs {
     float eps;
 };
 
-// One warp per token row (no block-wide waits); a lane takes groups of VEC neighbouring columns (VEC 4: 16-byte loads
-// and stores, for widths that are multiples of four). The norm's input waits in shared memory between the passes
-// (mean, then the mean of the squared deviations, then the store); each lane reads back only what it wrote.
-#define SN_WARPS 4
-template <int VEC>
-__global__ void __launch_bounds__(SN_WARPS * 32) streams_norm_kernel(HcArgs a) {
-    extern __shared__ __align__(16) float u_all[];     // [SN_WARPS][W rounded up to 4]
+// One block per token row; a thread takes groups of VEC neighbouring columns (VEC 4: 16-byte loads and stores, for
+// widths that are multiples of four), so that a row's loads are all in flight at once. The norm's input waits in
+// shared memory between the passes (mean, then the mean of the squared deviations, then the store); each thread reads
+// back only what it wrote.
+template <int VEC, int SMAX>
+__global__ void __launch_bounds__(256, SMAX <= 2 ? 6 : SMAX <= 4 ? 3 : 1) streams_norm_kernel(HcArgs a) {
+    extern __shared__ __align__(16) float u[];         // [W rounded up to 4]
+    __shared__ float red[32];
     __shared__ float cm[HC_MAX_STREAMS * HC_MAX_STREAMS], co[HC_MAX_STREAMS], ci[HC_MAX_STREAMS];
     const int S = a.S, W = a.W;
-    if (threadIdx.x < S * S) cm[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.0f : 0.0f);
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) cm[i] = a.mix ? a.mix[i] : (i / S == i % S ? 1.0f : 0.0f);
     if (threadIdx.x < S) {
         co[threadIdx.x] = a.outc ? a.outc[threadIdx.x] : 1.0f;
         ci[threadIdx.x] = a.inc ? a.inc[threadIdx.x] : 1.0f;
     }
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = blockIdx.x * SN_WARPS + warp;
-    if (r >= a.n_rows) return;
-    float* u = u_all + (size_t)warp * ((W + 3) / 4 * 4);
+    const int r = blockIdx.x;
     const size_t row = a.rows ? (size_t)a.rows[r] : (size_t)r;
     float* xr = a.x + row * S * W;
     float part = 0.0f;
-    for (int c = lane * VEC; c < W; c += 32 * VEC) {
-        float xs[HC_MAX_STREAMS][VEC];
+    for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
+        float xs[SMAX][VEC];
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s) {
+        for (int s = 0; s < SMAX; ++s) {
             if (s >= S) break;
             if (VEC == 4) {
                 const float4 v = *(const float4*)(xr + (size_t)s * W + c);
@@ -85,21 +83,21 @@ __global__ void __launch_bounds__(SN_WARPS * 32) streams_norm_kernel(HcArgs a) {
                 yv[0] = a.y[row * W + c];
                 a.y[row * W + c] = 0.0f;
             }
-            float nx[HC_MAX_STREAMS][VEC];
+            float nx[SMAX][VEC];
 #pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+            for (int t = 0; t < SMAX; ++t) {
                 if (t >= S) break;
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) {
                     float v = 0.0f;
 #pragma unroll
-                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                    for (int s = 0; s < SMAX; ++s)
                         if (s < S) v = fmaf(cm[s * S + t], xs[s][i], v);
                     nx[t][i] = fmaf(co[t], yv[i], v);
                 }
             }
 #pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+            for (int t = 0; t < SMAX; ++t) {
                 if (t >= S) break;
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) xs[t][i] = nx[t][i];
@@ -112,7 +110,7 @@ __global__ void __launch_bounds__(SN_WARPS * 32) streams_norm_kernel(HcArgs a) {
             for (int i = 0; i < VEC; ++i) {
                 float v = 0.0f;
 #pragma unroll
-                for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                for (int s = 0; s < SMAX; ++s)
                     if (s < S) v = fmaf(ci[s], xs[s][i], v);
                 u[c + i] = v;
                 part += v;
@@ -120,17 +118,17 @@ __global__ void __launch_bounds__(SN_WARPS * 32) streams_norm_kernel(HcArgs a) {
         }
     }
     if (!a.w) return;
-    const float mean = sp_warp_sum(part) / (float)W;
+    const float mean = sp_block_sum(part, red) / (float)W;
     float dev = 0.0f;
-    for (int c = lane * VEC; c < W; c += 32 * VEC)
+    for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC)
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
             const float dlt = u[c + i] - mean;
             dev = fmaf(dlt, dlt, dev);
         }
-    const float var = sp_warp_sum(dev) / (float)W;
+    const float var = sp_block_sum(dev, red) / (float)W;
     const float inv = 1.0f / sqrtf(var + a.eps);
-    for (int c = lane * VEC; c < W; c += 32 * VEC) {
+    for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
         float o[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) o[i] = (u[c + i] - mean) * inv * sp_ld_dt(a.w, a.w_dt, c + i);
@@ -153,19 +151,29 @@ SP_API int sp_streams_norm(float* x, float* y, const float* mix, const float* ou
     if (n_rows <= 0) return 0;
     if (S < 1 || S > HC_MAX_STREAMS) SP_FAIL("streams_norm: %d streams, this kernel takes 1 to %d", S, HC_MAX_STREAMS);
     if (y && rows) SP_FAIL("streams_norm: an update runs over all rows");
-    const size_t smem = (size_t)SN_WARPS * ((W + 3) / 4 * 4) * sizeof(float);
+    const size_t smem = (size_t)((W + 3) / 4 * 4) * sizeof(float);
     if (smem > 200 * 1024) SP_FAIL("streams_norm: a row of %d does not fit shared memory", W);
     if (smem > 48 * 1024 && !streams_norm_ready.done()) {
-        if (cudaFuncSetAttribute(streams_norm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
-            cudaFuncSetAttribute(streams_norm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(streams_norm_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(streams_norm_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(streams_norm_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(streams_norm_kernel<4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(streams_norm_kernel<1, HC_MAX_STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(streams_norm_kernel<4, HC_MAX_STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
             SP_FAIL("streams_norm: cannot raise the shared memory limit");
         streams_norm_ready.mark();
     }
     HcArgs a{x, y, mix, outc, inc, w, w_dt, out, out_dt, rows, n_rows, S, W, eps};
     const bool wide = W % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)out)) & 15) == 0;
-    const int blocks = (n_rows + SN_WARPS - 1) / SN_WARPS;
-    if (wide) streams_norm_kernel<4><<<blocks, SN_WARPS * 32, smem, stream>>>(a);
-    else streams_norm_kernel<1><<<blocks, SN_WARPS * 32, smem, stream>>>(a);
+    const int groups = wide ? W / 4 : W;
+    int threads = (groups + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : threads > 256 ? 256 : threads;
+    if (wide && S <= 2) streams_norm_kernel<4, 2><<<n_rows, threads, smem, stream>>>(a);
+    else if (S <= 2) streams_norm_kernel<1, 2><<<n_rows, threads, smem, stream>>>(a);
+    else if (wide && S <= 4) streams_norm_kernel<4, 4><<<n_rows, threads, smem, stream>>>(a);
+    else if (wide) streams_norm_kernel<4, HC_MAX_STREAMS><<<n_rows, threads, smem, stream>>>(a);
+    else if (S <= 4) streams_norm_kernel<1, 4><<<n_rows, threads, smem, stream>>>(a);
+    else streams_norm_kernel<1, HC_MAX_STREAMS><<<n_rows, threads, smem, stream>>>(a);
     SP_CHECK_LAUNCH("streams_norm");
     return 0;
 }
@@ -306,6 +314,112 @@ __global__ void __launch_bounds__(CQ_WARPS * 32) conv_qk_store_kernel(CqArgs a) 
     }
 }
 
+// The same for sizes that are multiples of four (head sizes, half the rotated dims, the row strides): a lane takes four
+// neighbouring dims with 16-byte loads and 8- or 16-byte stores, eight warps share a token's heads.
+#define CQV_WARPS 8
+__device__ __forceinline__ void cq_store4(void* p, int dt, size_t i, float4 v) {
+    if (dt == SP_DT_F32) {
+        *(float4*)((float*)p + i) = v;
+    } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        *(uint2*)((__nv_bfloat16*)p + i) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+    }
+}
+
+__global__ void __launch_bounds__(CQV_WARPS * 32) conv_qk_store_vec_kernel(CqArgs a) {
+    __shared__ __align__(16) float hv[CQV_WARPS][CQ_MAX_DIM];
+    __shared__ __align__(16) float cs[2][CQ_MAX_DIM / 2];
+    const int t = blockIdx.x;
+    if (t >= a.T) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = a.token_seq[t];
+    const int pos = a.positions[t];
+    const int local = t - a.seq_start[s];
+    const int slot = a.seq_slot[s];
+    if (a.taps > 1 && (slot < 0 || slot >= a.n_slots)) return;
+    const int half = a.rd >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * a.inv_freq[i];
+        cs[0][i] = cosf(ang);
+        cs[1][i] = sinf(ang);
+    }
+    __syncthreads();
+    const int d = a.d, vd = a.vd, nh = a.nh, nkv = a.nkv, n = a.taps - 1;
+    const int C = (nh + nkv) * d + nkv * vd;
+    bool place = true;
+    int page = 0;
+    {
+        const int row = a.seq_row[s];
+        if (!sp_index_ok(row, a.rg.n_rows, a.rg, 402) || !sp_index_ok(pos / a.page_size, a.max_pages, a.rg, 403)) place = false;
+        else {
+            page = a.page_table[(size_t)row * a.max_pages + pos / a.page_size];
+            place = sp_index_ok(page, a.rg.n_pages, a.rg, 401);
+        }
+    }
+    const int off = pos % a.page_size;
+    float* st = a.taps > 1 ? a.state + (size_t)slot * n * C : nullptr;
+    for (int hh = warp; hh < nh + 2 * nkv; hh += CQV_WARPS) {
+        const bool is_v = hh >= nh + nkv;
+        const int size = is_v ? vd : d;
+        const int cb = is_v ? (nh + nkv) * d + (hh - nh - nkv) * vd : hh * d;
+        __syncwarp();
+        for (int i = lane * 4; i < size; i += 128) {
+            const int c = cb + i;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int j = 0; j < a.taps; ++j) {
+                const int l = local - n + j;
+                const float4 u = l >= 0 ? *(const float4*)(a.qkv + (size_t)(t - n + j) * a.ld + c) : *(const float4*)(st + (size_t)(n + l) * C + c);
+                if (a.conv) {
+                    acc.x = fmaf(sp_ld_dt(a.conv, a.conv_dt, (size_t)c * a.taps + j), u.x, acc.x);
+                    acc.y = fmaf(sp_ld_dt(a.conv, a.conv_dt, (size_t)(c + 1) * a.taps + j), u.y, acc.y);
+                    acc.z = fmaf(sp_ld_dt(a.conv, a.conv_dt, (size_t)(c + 2) * a.taps + j), u.z, acc.z);
+                    acc.w = fmaf(sp_ld_dt(a.conv, a.conv_dt, (size_t)(c + 3) * a.taps + j), u.w, acc.w);
+                } else {
+                    acc = u;
+                }
+                if (a.save_inline && j >= 1) *(float4*)(st + (size_t)(j - 1) * C + c) = u;     // local is 0: row j was read first
+            }
+            *(float4*)&hv[warp][i] = acc;
+        }
+        __syncwarp();
+        if (is_v) {
+            if (place) {
+                const size_t vb = (((size_t)page * nkv + (hh - nh - nkv)) * a.page_size + off) * vd;
+                for (int i = lane * 4; i < vd; i += 128) {
+                    const float4 v = *(const float4*)&hv[warp][i];
+                    cq_store4(a.vpool, a.cache_dt, vb + i, make_float4(v.x * a.v_scale, v.y * a.v_scale, v.z * a.v_scale, v.w * a.v_scale));
+                }
+            }
+            continue;
+        }
+        for (int i = lane * 4; i < half; i += 128) {
+            const float4 x0 = *(const float4*)&hv[warp][i], x1 = *(const float4*)&hv[warp][i + half];
+            const float4 co = *(const float4*)&cs[0][i], si = *(const float4*)&cs[1][i];
+            *(float4*)&hv[warp][i] = make_float4(x0.x * co.x - x1.x * si.x, x0.y * co.y - x1.y * si.y, x0.z * co.z - x1.z * si.z, x0.w * co.w - x1.w * si.w);
+            *(float4*)&hv[warp][i + half] = make_float4(x1.x * co.x + x0.x * si.x, x1.y * co.y + x0.y * si.y, x1.z * co.z + x0.z * si.z, x1.w * co.w + x0.w * si.w);
+        }
+        __syncwarp();
+        float inv = 1.0f;
+        if (a.unit_rms) {
+            float ss = 0.0f;
+            for (int i = lane * 4; i < d; i += 128) {
+                const float4 v = *(const float4*)&hv[warp][i];
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = sp_warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)d + a.eps);
+        }
+        if (hh >= nh && !place) continue;
+        void* dst = hh < nh ? a.q_out : a.kpool;
+        const int dt = hh < nh ? a.q_dt : a.cache_dt;
+        const size_t base = hh < nh ? (size_t)t * nh * d + (size_t)hh * d : (((size_t)page * nkv + (hh - nh)) * a.page_size + off) * d;
+        for (int i = lane * 4; i < d; i += 128) {
+            const float4 v = *(const float4*)&hv[warp][i];
+            cq_store4(dst, dt, base + i, make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv));
+        }
+    }
+}
+
 // the state after a step of several tokens per sequence: the last taps−1 projected values of each sequence, the
 // older ones moved down where the step brought fewer (rows ascending: a row only reads rows above itself)
 __global__ void conv_state_save_kernel(CqArgs a, int B, int C) {
@@ -336,7 +450,10 @@ SP_API int sp_conv_qk_store(const float* qkv, int ld, const void* conv, int conv
     CqArgs a{qkv, ld, conv, conv_dt, taps, state, n_slots, inv_freq, rd, q_out, q_dt, kpool, vpool, cache_dt,
              token_seq, positions, seq_row, page_table, max_pages, page_size, seq_start, seq_slot, T, nh, nkv, d, vd,
              eps, v_scale, unit_rms, (all_single && taps > 1) ? 1 : 0, sp_range_host};
-    conv_qk_store_kernel<<<T, CQ_WARPS * 32, 0, stream>>>(a);
+    const bool wide = d % 4 == 0 && vd % 4 == 0 && (rd / 2) % 4 == 0 && ld % 4 == 0 &&
+                      ((((uintptr_t)qkv) | ((uintptr_t)state) | ((uintptr_t)q_out) | ((uintptr_t)kpool) | ((uintptr_t)vpool)) & 15) == 0;
+    if (wide) conv_qk_store_vec_kernel<<<T, CQV_WARPS * 32, 0, stream>>>(a);
+    else conv_qk_store_kernel<<<T, CQ_WARPS * 32, 0, stream>>>(a);
     SP_CHECK_LAUNCH("conv_qk_store");
     if (taps > 1 && !all_single) {
         const int C = (nh + nkv) * d + nkv * vd;
