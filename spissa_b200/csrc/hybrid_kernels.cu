@@ -1139,7 +1139,11 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int* 
 
 __global__ void __launch_bounds__(256)
 moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict__ counts, int E, int* __restrict__ sorted,
-                 int* __restrict__ tiles /* [max_tiles][3] */, int max_tiles, int tm) {
+                 int* __restrict__ tiles /* [max_tiles][3] */, int max_tiles, int tm, int padded, int* __restrict__ pos,
+                 int* __restrict__ tab_up, int* __restrict__ tab_down, int up_rows, int down_rows) {
+    // ``padded``: every expert's rows begin at a tile's first row (the sorted list then has holes, which say -1, and
+    // ``pos`` gives every pair its row); ``tab_up`` / ``tab_down``: per tile the row at which the expert's matrices begin
+    // in the stacked weights (-1: the tile is not in use), for products that take whole tiles of one expert.
     __shared__ int start, tile0, mine, wsum[8], running;
     const int e = blockIdx.x;
     if (threadIdx.x == 0) {
@@ -1157,7 +1161,11 @@ moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict
         __syncthreads();
         int before = running;
         for (int w = 0; w < warp; ++w) before += wsum[w];
-        if (hit) sorted[start + before + __popc(b & ((1u << lane) - 1u))] = p;
+        if (hit) {
+            const int at = (padded ? tile0 * tm : start) + before + __popc(b & ((1u << lane) - 1u));
+            sorted[at] = p;
+            if (pos) pos[p] = at;
+        }
         __syncthreads();
         if (threadIdx.x == 0) {
             int tot = 0;
@@ -1170,11 +1178,15 @@ moe_place_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict
     for (int i = threadIdx.x; i < n_mine; i += blockDim.x) {
         if (tile0 + i >= max_tiles) break;
         tiles[(tile0 + i) * 3 + 0] = e;
-        tiles[(tile0 + i) * 3 + 1] = start + i * tm;
+        tiles[(tile0 + i) * 3 + 1] = (padded ? tile0 * tm : start) + i * tm;
         tiles[(tile0 + i) * 3 + 2] = min(tm, mine - i * tm);
+        if (tab_up) { tab_up[tile0 + i] = e * up_rows; tab_down[tile0 + i] = e * down_rows; }
     }
     if (e == E - 1)
-        for (int i = tile0 + n_mine + threadIdx.x; i < max_tiles; i += blockDim.x) tiles[i * 3] = -1;
+        for (int i = tile0 + n_mine + threadIdx.x; i < max_tiles; i += blockDim.x) {
+            tiles[i * 3] = -1;
+            if (tab_up) { tab_up[i] = -1; tab_down[i] = -1; }
+        }
 }
 
 SP_API int sp_moe_tile_rows() { return ME_TM; }          // the smallest tile any path uses: sizes the tile table
@@ -1183,8 +1195,70 @@ static int moe_plan(const int* ids, int n_pairs, int E, int* counts, int* sorted
                     cudaStream_t stream) {
     moe_count_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts);
     SP_CHECK_LAUNCH("moe_count");
-    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, tm);
+    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, tm, 0, nullptr, nullptr, nullptr, 0, 0);
     SP_CHECK_LAUNCH("moe_place");
+    return 0;
+}
+
+// The plan for products that take whole 128-row tiles of one expert (the tcgen05 tile kernel's grouped form), and the
+// rows in that order: sorted [max_tiles·128] (holes -1), pos [n_pairs], tab_up / tab_down [max_tiles], xs [max_tiles·128][W].
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted,
+                                       __nv_bfloat16* __restrict__ xs, int rows, int top, int W) {
+    const int per = W / 8;                                       // 16-byte pieces of a row
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)rows * per; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / per), c = (int)(i % per);
+        const int p = sorted[r];
+        ((uint4*)xs)[i] = p >= 0 ? ((const uint4*)(x + (size_t)(p / top) * W))[c] : make_uint4(0, 0, 0, 0);
+    }
+}
+
+SP_API int sp_moe_plan_tiles(const void* x, const int* ids, int T, int top, int W, int E, int up_rows, int down_rows, int* counts,
+                             int* sorted, int* pos, int* tiles, int* tab_up, int* tab_down, int max_tiles, void* xs,
+                             cudaStream_t stream) {
+    const int n_pairs = T * top;
+    if (n_pairs <= 0) return 0;
+    if (W % 8 || (((uintptr_t)x | (uintptr_t)xs) & 15)) SP_FAIL("moe_plan_tiles: rows of %d do not move in 16-byte pieces", W);
+    if ((n_pairs + 127) / 128 + E > max_tiles) SP_FAIL("moe_plan_tiles: the tile table is too short");
+    SP_CHECK_CALL("moe_plan_tiles", cudaMemsetAsync(sorted, 0xff, (size_t)max_tiles * 128 * sizeof(int), stream));
+    moe_count_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts);
+    SP_CHECK_LAUNCH("moe_count");
+    moe_place_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts, E, sorted, tiles, max_tiles, 128, 1, pos, tab_up, tab_down, up_rows, down_rows);
+    SP_CHECK_LAUNCH("moe_place");
+    const size_t n = (size_t)max_tiles * 128 * (W / 8);
+    const size_t want = (n + 255) / 256;
+    moe_gather_rows_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(
+        (const __nv_bfloat16*)x, sorted, (__nv_bfloat16*)xs, max_tiles * 128, top, W);
+    SP_CHECK_LAUNCH("moe_gather_rows");
+    return 0;
+}
+
+// y[t] += Σ_k weight[t·top + k] · rows[pos[t·top + k]] in the order of k
+__global__ void moe_combine_rows_kernel(const float* __restrict__ rows, const int* __restrict__ pos, const float* __restrict__ wts,
+                                        float* __restrict__ y, size_t T, int top, int W) {
+    const size_t n = T * (size_t)(W / 4);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / (W / 4);
+        const int c = (int)(i % (W / 4));
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int k = 0; k < top; ++k) {
+            const float wt = wts[t * top + k];
+            const float4 r = ((const float4*)(rows + (size_t)pos[t * top + k] * W))[c];
+            v.x += r.x * wt; v.y += r.y * wt; v.z += r.z * wt; v.w += r.w * wt;
+        }
+        float4 o = ((float4*)(y + t * W))[c];
+        o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+        ((float4*)(y + t * W))[c] = o;
+    }
+}
+
+SP_API int sp_moe_combine_rows(const float* rows, const int* pos, const float* wts, float* y, int T, int top, int W,
+                               cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (W % 4 || (((uintptr_t)rows | (uintptr_t)y) & 15)) SP_FAIL("moe_combine_rows: rows of %d do not move in 16-byte pieces", W);
+    const size_t n = (size_t)T * (W / 4);
+    const size_t want = (n + 255) / 256;
+    moe_combine_rows_kernel<<<(unsigned)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>(rows, pos, wts, y, (size_t)T, top, W);
+    SP_CHECK_LAUNCH("moe_combine_rows");
     return 0;
 }
 
@@ -1320,7 +1394,9 @@ __global__ void __launch_bounds__(128)
 moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ Wt, long long w_stride,
                int N, int K, const int* __restrict__ sorted, const int* __restrict__ tiles, int top,
                __nv_bfloat16* __restrict__ act, float* __restrict__ out, const float* __restrict__ wts, float limit,
-               float slope) {
+               float slope, int blk) {
+    // ``blk`` (GLU): 0 = an expert's N gate rows, then its N up rows; else blocks of ``blk`` gate rows, each followed by
+    // the ``blk`` up rows of the same outputs (the layout the tcgen05 tile kernel's gated epilogue reads)
     __shared__ __align__(16) __nv_bfloat16 As[2][MM_TM][MM_ROW];
     __shared__ __align__(16) __nv_bfloat16 Bs[2][GLU ? 2 : 1][MM_BN][MM_ROW];
     __shared__ int src_row[MM_TM];
@@ -1344,7 +1420,9 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
         }
         for (int c = threadIdx.x; c < (GLU ? 2 : 1) * MM_BN * 4; c += 128) {
             const int m = c / (MM_BN * 4), r = (c >> 2) % MM_BN, k = kb * MM_BK + (c & 3) * 8;
-            if (n0 + r < N && k < K) cp_async16(smem_u32(&Bs[st][m][r][(c & 3) * 8]), w0 + ((size_t)m * N + n0 + r) * K + k);
+            const int n = n0 + r;
+            const size_t w_row = blk ? (size_t)(n / blk) * 2 * blk + n % blk + (size_t)m * blk : (size_t)m * N + n;
+            if (n < N && k < K) cp_async16(smem_u32(&Bs[st][m][r][(c & 3) * 8]), w0 + w_row * K + k);
             else *(uint4*)&Bs[st][m][r][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
         }
         cp_async_commit();
@@ -1422,9 +1500,12 @@ __global__ void moe_combine_kernel(const float* __restrict__ out, float* __restr
 
 SP_API int sp_moe_experts(const void* x, int x_dt, const int* ids, const void* wgu, const void* wd, int w_dt, int E,
                           int* counts, int* sorted, int* tiles, int max_tiles, const float* wts, void* act, float* out_pairs,
-                          float* y, int T, int top, int W, int F, float limit, float slope, cudaStream_t stream) {
+                          float* y, int T, int top, int W, int F, float limit, float slope, int glu_block,
+                          cudaStream_t stream) {
     if (T <= 0) return 0;
     const int n_pairs = T * top;
+    if (glu_block && (x_dt != SP_DT_BF16 || w_dt != SP_DT_BF16 || F % glu_block))
+        SP_FAIL("moe_experts: gate and up rows in blocks of %d are a bfloat16 layout for sizes that are multiples of it", glu_block);
     const bool mma = x_dt == SP_DT_BF16 && w_dt == SP_DT_BF16 && W % 8 == 0 && F % 8 == 0 &&
                      (((uintptr_t)x | (uintptr_t)wgu | (uintptr_t)wd | (uintptr_t)act) & 15) == 0;
     const int tm = mma ? MM_TM : ME_TM;
@@ -1434,13 +1515,14 @@ SP_API int sp_moe_experts(const void* x, int x_dt, const int* ids, const void* w
         const int used = (n_pairs + tm - 1) / tm + E;           // entries beyond the tiles in use say expert -1
         moe_mma_kernel<true><<<dim3(used, (F + MM_BN - 1) / MM_BN), 128, 0, stream>>>(
             (const __nv_bfloat16*)x, W, (const __nv_bfloat16*)wgu, 2LL * F * W, F, W, sorted, tiles, top,
-            (__nv_bfloat16*)act, nullptr, nullptr, limit, slope);
+            (__nv_bfloat16*)act, nullptr, nullptr, limit, slope, glu_block);
         SP_CHECK_LAUNCH("moe_up (tensor cores)");
         moe_mma_kernel<false><<<dim3(used, (W + MM_BN - 1) / MM_BN), 128, 0, stream>>>(
             (const __nv_bfloat16*)act, F, (const __nv_bfloat16*)wd, (long long)W * F, W, F, sorted, tiles, top, nullptr,
-            out_pairs, wts, 0.0f, 0.0f);
+            out_pairs, wts, 0.0f, 0.0f, 0);
         SP_CHECK_LAUNCH("moe_down (tensor cores)");
     } else {
+        if (glu_block) SP_FAIL("moe_experts: sizes that the tensor-core tiles do not take need the plain layout of gate and up rows");
         const dim3 g_up(max_tiles, (F + ME_BN - 1) / ME_BN), g_down(max_tiles, (W + ME_BN - 1) / ME_BN);
 #define ME_LAUNCH(TA, TW)                                                                                             \
     do {                                                                                                              \

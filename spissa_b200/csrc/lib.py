@@ -1127,29 +1127,61 @@ def moe_tile_rows() -> int:
     return int(load("hybrid").sp_moe_tile_rows())
 
 
-def moe_experts(x, ids, weights, w_gate_up, w_down, y, top, limit, slope=1.702):
+TC_EXPERT_PAIRS = 512        # from this many (token, expert) pairs on, and 8 per expert, whole 128-row tiles pay off
+
+
+def moe_experts(x, ids, weights, w_gate_up, w_down, y, top, limit, slope=1.702, glu_block=0):
     """y (float32 [T, W]) += Σ_k weights[t,k] · expert_{ids[t,k]}(x[t]) with clamped-GLU experts: ``w_gate_up``
-    [E, 2F, W] (gate rows, then up rows), ``w_down`` [E, W, F]. The (token, expert) pairs are sorted by expert on the
-    device; nothing comes back to the host."""
+    [E, 2F, W] (an expert's gate rows, then its up rows; with ``glu_block`` = b: blocks of b gate rows, each followed by
+    the b up rows of the same outputs), ``w_down`` [E, W, F]. The (token, expert) pairs are sorted by expert on the
+    device; nothing comes back to the host. Many pairs in the block layout: the products run as grouped products of the
+    tcgen05 tile kernel over rows gathered into 128-row tiles of one expert each."""
     lib = load("hybrid")
     _need_contig(x, ids, weights, w_gate_up, w_down, y)
     T, W = x.shape
     E, F2, _ = w_gate_up.shape
     F = F2 // 2
     n_pairs = T * top
-    tm = moe_tile_rows()
-    max_tiles = (n_pairs + tm - 1) // tm + E
     dev = x.device
-    book = torch.empty(E + n_pairs + 3 * max_tiles, dtype=torch.int32, device=dev)
-    counts, order, tiles = book[:E], book[E:E + n_pairs], book[E + n_pairs:]
     if ids.dtype != torch.int32 or weights.dtype != torch.float32 or y.dtype != torch.float32:
         raise KernelError("moe_experts takes int32 ids, float32 weights and adds into a float32 matrix")
+    global launches
+    if (glu_block and n_pairs >= max(TC_EXPERT_PAIRS, 8 * E) and W % 128 == 0 and F % 8 == 0 and W % 4 == 0
+            and tc_gemm_supported(x, w_gate_up[0]) and w_down.dtype == torch.bfloat16):
+        tc = load("tc_gemm")
+        max_tiles = (n_pairs + 127) // 128 + E
+        rows = max_tiles * 128
+        book = torch.empty(E + rows + n_pairs + 5 * max_tiles, dtype=torch.int32, device=dev)
+        counts, order, pos = book[:E], book[E:E + rows], book[E + rows:E + rows + n_pairs]
+        rest = book[E + rows + n_pairs:]
+        tiles, tab_up, tab_down = rest[:3 * max_tiles], rest[3 * max_tiles:4 * max_tiles], rest[4 * max_tiles:]
+        xs = torch.empty(rows, W, dtype=torch.bfloat16, device=dev)
+        act = torch.empty(rows, F, dtype=torch.bfloat16, device=dev)
+        out_rows = torch.empty(rows, W, dtype=torch.float32, device=dev)
+        launches += 6
+        _check("hybrid", lib.sp_moe_plan_tiles(
+            c_void_p(_ptr(x)), c_void_p(_ptr(ids)), T, int(top), W, E, 2 * F, W, c_void_p(_ptr(counts)), c_void_p(_ptr(order)),
+            c_void_p(_ptr(pos)), c_void_p(_ptr(tiles)), c_void_p(_ptr(tab_up)), c_void_p(_ptr(tab_down)), max_tiles,
+            c_void_p(_ptr(xs)), c_void_p(_stream())))
+        status = c_void_p(_ptr(status_word(dev)))
+        _check("tc_gemm", tc.sp_tc_gemm_grouped(
+            c_void_p(_ptr(xs)), c_void_p(_ptr(w_gate_up)), c_void_p(_ptr(act)), dt_code(act), rows, 2 * F, W, W, W, E * 2 * F, F,
+            TC_SILU_MUL, 2 * int(glu_block), c_void_p(_ptr(tab_up)), c_float(limit), c_float(slope), status, c_void_p(_stream())))
+        _check("tc_gemm", tc.sp_tc_gemm_grouped(
+            c_void_p(_ptr(act)), c_void_p(_ptr(w_down)), c_void_p(_ptr(out_rows)), dt_code(out_rows), rows, W, F, F, F, E * W, W,
+            TC_STORE, 128, c_void_p(_ptr(tab_down)), c_float(0.0), c_float(0.0), status, c_void_p(_stream())))
+        _check("hybrid", lib.sp_moe_combine_rows(c_void_p(_ptr(out_rows)), c_void_p(_ptr(pos)), c_void_p(_ptr(weights)),
+                                                 c_void_p(_ptr(y)), T, int(top), W, c_void_p(_stream())))
+        return
+    tm = moe_tile_rows()
+    max_tiles = (n_pairs + tm - 1) // tm + E
+    book = torch.empty(E + n_pairs + 3 * max_tiles, dtype=torch.int32, device=dev)
+    counts, order, tiles = book[:E], book[E:E + n_pairs], book[E + n_pairs:]
     act = torch.empty(n_pairs, F, dtype=x.dtype, device=dev)
     out_pairs = torch.empty(n_pairs, W, dtype=torch.float32, device=dev)
-    global launches
     launches += 4
     _check("hybrid", lib.sp_moe_experts(
         c_void_p(_ptr(x)), dt_code(x), c_void_p(_ptr(ids)), c_void_p(_ptr(w_gate_up)), c_void_p(_ptr(w_down)),
         _w_dt(w_gate_up, w_down), E, c_void_p(_ptr(counts)), c_void_p(_ptr(order)), c_void_p(_ptr(tiles)), max_tiles,
         c_void_p(_ptr(weights)), c_void_p(_ptr(act)), c_void_p(_ptr(out_pairs)), c_void_p(_ptr(y)), T, int(top), W, F,
-        c_float(limit), c_float(slope), c_void_p(_stream())))
+        c_float(limit), c_float(slope), int(glu_block), c_void_p(_stream())))

@@ -174,7 +174,12 @@ template <int BN, int STAGES, int CG = 1>
 __global__ void __launch_bounds__(192, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ C, int c_dt, int M, int N, int K, int ldc, int mode, int* status,
-               const __grid_constant__ EpiArgs ep, const SpRange rg) {
+               const __grid_constant__ EpiArgs ep, const SpRange rg, const int* __restrict__ group, float glu_limit,
+               float glu_slope) {
+    // ``group`` (single CTAs only): a grouped product. The rows of A lie sorted by group in tiles of 128 rows; entry
+    // t of the table is the row of W at which the weights of row tile t's group begin (W stacks the groups' matrices,
+    // N rows each), or -1 for a row tile that is not in use, which all three roles pass over alike. ``glu_slope``
+    // non-zero: the gated epilogue is g·sigmoid(slope·g)·(u + 1) with g = min(gate, limit), u = clamp(up, ±limit).
     using L = SmemLayout<BN, STAGES, CG>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -234,6 +239,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t kbc = 0;                                   // pipeline slots used so far, over all tiles
             bool ok = true;
             for (int tile = walker; tile < total_tiles && ok; tile += walkers) {
+                const int w_row = group ? group[tile % m_tiles] : 0;
+                if (w_row < 0) continue;
                 const int m0 = (tile % m_tiles) * TM + rank * BM, n0 = (tile / m_tiles) * BN + rank * (BN / CG);
                 for (int kb = 0; kb < num_kb; ++kb, ++kbc) {
                     const int s = kbc % STAGES;
@@ -251,7 +258,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     } else {
                         mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
                         tma_load_2d(a_dst, &map_a, kb * BK, m0, smem_u32(&bar_full[s]));
-                        tma_load_2d(b_dst, &map_w, kb * BK, n0, smem_u32(&bar_full[s]));
+                        tma_load_2d(b_dst, &map_w, kb * BK, n0 + w_row, smem_u32(&bar_full[s]));
                     }
                 }
             }
@@ -262,6 +269,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t kbc = 0, it = 0;
             bool ok = true;
             for (int tile = walker; tile < total_tiles && ok; tile += walkers, ++it) {
+                if (group && group[tile % m_tiles] < 0) { --it; continue; }      // not in use: no accumulator is taken
                 const uint32_t buf = it & 1u, use = it >> 1;
                 ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), (use & 1u) ^ 1u, status, 104);
                 if (!ok) break;
@@ -298,6 +306,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             else mbar_arrive(smem_u32(&bar_acc_empty[buf]));
         };
         for (int tile = walker; tile < total_tiles; tile += walkers, ++it) {
+            if (group && group[tile % m_tiles] < 0) { --it; continue; }
             const int m0 = (tile % m_tiles) * TM + rank * BM, n0 = (tile / m_tiles) * BN;
             const uint32_t buf = it & 1u, use = it >> 1;
             const int row = m0 + q * 32 + lane;
@@ -503,8 +512,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tc_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const float g = __uint_as_float(r[j]) * rstd;
-                        v[j] = (g / (1.0f + expf(-g))) * (__uint_as_float(u[j]) * rstd);
+                        float g = __uint_as_float(r[j]) * rstd;
+                        if (glu_slope != 0.0f) {
+                            g = fminf(g, glu_limit);
+                            const float up = fminf(fmaxf(__uint_as_float(u[j]) * rstd, -glu_limit), glu_limit);
+                            v[j] = (g / (1.0f + expf(-glu_slope * g))) * (up + 1.0f);
+                        } else {
+                            v[j] = (g / (1.0f + expf(-g))) * (__uint_as_float(u[j]) * rstd);
+                        }
                     }
                 } else {
                     tc_ld_wait();
@@ -787,7 +802,31 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int 
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     SP_CHECK_CALL("tc_gemm", sp_launch_dependent(tc_gemm_kernel<BN, STAGES>, dim3(grid), dim3(192), (size_t)L::TOTAL, stream, ma, mw,
-                                                 C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host));
+                                                 C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host, (const int*)nullptr,
+                                                 0.0f, 0.0f));
+    return 0;
+}
+
+// A grouped product (see the kernel's ``group``): every row tile takes its own group's weights
+template <int BN, int STAGES>
+int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int M, int N, int K, int ldc, int mode,
+                   int* status, cudaStream_t stream, const int* group, float limit, float slope) {
+    using L = SmemLayout<BN, STAGES>;
+    static SpPerDevice configured;
+    if (!configured.done()) {
+        cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("tc_gemm: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+        configured.mark();
+    }
+    const int sm_count = sp_sm_count();
+    if (sm_count <= 0) SP_FAIL("tc_gemm: cannot read the number of SMs");
+    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int grid = (int)(tiles < sm_count ? tiles : sm_count);
+    EpiArgs ep;
+    memset(&ep, 0, sizeof(ep));
+    SP_CHECK_CALL("tc_gemm (grouped)", sp_launch_dependent(tc_gemm_kernel<BN, STAGES>, dim3(grid), dim3(192), (size_t)L::TOTAL, stream,
+                                                           ma, mw, C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host, group,
+                                                           limit, slope));
     return 0;
 }
 
@@ -808,7 +847,8 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw_half, void* C, int 
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
     const int pairs = (int)(tiles < sm_count / 2 ? tiles : sm_count / 2);
     SP_CHECK_CALL("tc_gemm", sp_launch_cluster(tc_gemm_kernel<BN, STAGES, 2>, dim3(2 * pairs), dim3(192), (size_t)L::TOTAL, stream,
-                                               -2, ma, mw_half, C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host));
+                                               -2, ma, mw_half, C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host,
+                                               (const int*)nullptr, 0.0f, 0.0f));
     return 0;
 }
 
@@ -883,6 +923,27 @@ SP_API int sp_tc_gemm(const void* A, const void* W, void* C, int c_dt, int M, in
                       int mode, int bn, int* status, cudaStream_t stream) {
     if (mode == MODE_QKV_ROPE) SP_FAIL("tc_gemm: the rotate-and-store epilogue needs sp_tc_gemm_fused");
     return tc_gemm_any(A, W, C, c_dt, M, N, K, lda, ldw, ldc, mode, bn, nullptr, status, stream);
+}
+
+// A grouped product on 128-row tiles of A (M a multiple of 128): row tile t multiplies with the N rows of W that begin
+// at row group[t] (W [w_rows, K] stacks the groups' matrices), or is passed over when group[t] < 0. mode 0: C [M, N];
+// mode 2: the groups' gate and up rows interleaved in blocks of bn/2, C [M, N/2] = the gated activation, clamped when
+// ``slope`` is non-zero. Nothing about the groups is known to the host.
+SP_API int sp_tc_gemm_grouped(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw,
+                              int w_rows, int ldc, int mode, int bn, const int* group, float limit, float slope,
+                              int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (sp_tc_gemm_supported(A, W, K, lda, ldw)) return 1;
+    if (M % BM) SP_FAIL("tc_gemm (grouped): the rows (%d) come in tiles of %d", M, BM);
+    if (mode != MODE_STORE && mode != MODE_SILU_MUL) SP_FAIL("tc_gemm (grouped): mode %d is not built", mode);
+    if (bn != 128 && bn != 256) SP_FAIL("tc_gemm (grouped): tile width %d is not built (128 or 256)", bn);
+    if (N % bn) SP_FAIL("tc_gemm (grouped): a group's %d rows of W are no multiple of the tile width %d", N, bn);
+    if (!group) SP_FAIL("tc_gemm (grouped): the table of the row tiles' groups is missing");
+    CUtensorMap ma, mw;
+    if (make_map(&ma, A, M, K, lda, BM)) return 1;
+    if (make_map(&mw, W, w_rows, K, ldw, bn)) return 1;
+    if (bn == 128) return launch_grouped<128, 6>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, group, limit, slope);
+    return launch_grouped<256, 4>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, group, limit, slope);
 }
 
 static int tc_gemm_any(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,

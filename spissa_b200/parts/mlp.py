@@ -179,6 +179,7 @@ class RoutedExperts(FeedForward):
     expert i's tensors stand under ``expert_prefix`` + i + "." (``e0.gate`` …)."""
     graph_safe = True
     kernel_modules = ("hybrid",)
+    kernel_modules_bf16 = ("tc_gemm",)
 
     def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: float,
                  slope: float = 1.702, groups: int = 1, keep_groups: int = 1, shared=None, prefix: str = "",
@@ -218,9 +219,23 @@ class RoutedExperts(FeedForward):
         super().bind(tensors, rt)
         self.router = Linear(tensors[self.prefix + self.names["router"]])
         self.correction = tensors[self.prefix + self.names["correction"]].contiguous()
-        # [E, 2I, H]: an expert's gate rows, then its up rows; [E, H, I]
-        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]], dim=0)
-                                      for i in range(self.experts)]).contiguous()
+        # [E, 2I, H] and [E, H, I]. An expert's gate rows, then its up rows; for bfloat16 sizes that the tensor-core
+        # kernels take, in blocks (``glu_block`` gate rows, then the up rows of the same outputs), so that one tile of a
+        # product holds both halves and applies the activation in its epilogue
+        H, I = self.hidden_size, self.intermediate_size
+        gate0 = tensors[self._expert(0, "gate")]
+        self.glu_block = 0
+        if gate0.dtype == torch.bfloat16 and H % 8 == 0 and I % 64 == 0:
+            self.glu_block = 128 if I % 128 == 0 else 64
+        b = self.glu_block
+
+        def gate_up(i):
+            g, u = tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]
+            if not b:
+                return torch.cat([g, u], dim=0)
+            return torch.stack([g.reshape(I // b, b, H), u.reshape(I // b, b, H)], dim=1).reshape(2 * I, H)
+
+        self.w_gate_up = torch.stack([gate_up(i) for i in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(i, "down")] for i in range(self.experts)]).contiguous()
 
     def forward(self, x, step, residual):
@@ -231,6 +246,6 @@ class RoutedExperts(FeedForward):
             wts = torch.empty(T, self.top, dtype=torch.float32, device=x.device)
             K.moe_select(z, self.correction, ids, wts, self.top, self.groups, self.keep_groups)
         with phase("experts_ms"):
-            K.moe_experts(x, ids, wts, self.w_gate_up, self.w_down, residual, self.top, self.limit, self.slope)
+            K.moe_experts(x, ids, wts, self.w_gate_up, self.w_down, residual, self.top, self.limit, self.slope, self.glu_block)
         if self.shared is not None:
             self.shared.forward(x, step, residual)

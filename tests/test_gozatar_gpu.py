@@ -344,6 +344,41 @@ def test_experts_on_the_tensor_cores(T, W, F, E, top):
     assert torch.equal(y1[0], y[t])
 
 
+@pytest.mark.parametrize("T,W,F,E,top,blk", [(400, 128, 64, 4, 2, 64), (700, 256, 384, 8, 3, 128), (300, 128, 192, 16, 4, 64)])
+def test_experts_as_grouped_products_of_the_tile_kernel(T, W, F, E, top, blk):
+    """Many pairs, gate and up rows in blocks: rows gathered into 128-row tiles of one expert each, two grouped
+    products of the tcgen05 tile kernel, the weighted sum by a scatter map. The same weights with few pairs take the
+    mma.sync tiles (a decode step); both agree with the plain implementation."""
+    from spissa_b200.csrc import lib as K
+    g = torch.Generator().manual_seed(T + F)
+    limit = 0.9
+    x = torch.randn(T, W, generator=g).bfloat16()
+    w = {"router": torch.randn(E, W, generator=g) * 0.5, "correction": torch.zeros(E)}
+    for e in range(E):
+        for n, shape in (("gate", (F, W)), ("up", (F, W)), ("down", (W, F))):
+            w[f"e{e}.{n}"] = (torch.randn(shape, generator=g) * 0.3).bfloat16()
+    w["correction"][E - 1] = -10.0                              # an expert nobody chooses: its tiles are passed over
+    wd = {k: v.double() for k, v in w.items()}
+    r = dict(experts=E, top=top)
+    idx, wt = G.route(x.double(), wd, "", r)
+    assert E - 1 not in idx
+    ref = G.moe_ff(x.double(), wd, "", dict(router=r, expert=dict(limit=limit)))
+    gu = torch.stack([torch.stack([w[f"e{e}.gate"].reshape(F // blk, blk, W), w[f"e{e}.up"].reshape(F // blk, blk, W)], dim=1)
+                      .reshape(2 * F, W) for e in range(E)]).to(DEV).contiguous()
+    dn = torch.stack([w[f"e{e}.down"] for e in range(E)]).to(DEV)
+    ids, wts = idx.int().to(DEV).contiguous(), wt.float().to(DEV).contiguous()
+    y = torch.full((T, W), 0.5, device=DEV)
+    K.moe_experts(x.to(DEV), ids, wts, gu, dn, y, top, limit, glu_block=blk)
+    torch.cuda.synchronize()
+    K.check_status(torch.device(DEV))
+    assert worst(y - 0.5, ref) <= 8e-3
+    few = slice(T // 2, T // 2 + 5)
+    y5 = torch.zeros(5, W, device=DEV)
+    K.moe_experts(x[few].to(DEV), ids[few].contiguous(), wts[few].contiguous(), gu, dn, y5, top, limit, glu_block=blk)
+    assert worst(y5, ref[few]) <= 8e-3
+    assert worst(y5, (y - 0.5)[few].cpu()) <= 8e-3
+
+
 def test_activations_and_attention_with_values_of_another_size():
     from spissa_b200.csrc import lib as K
     g = torch.Generator().manual_seed(3)
