@@ -742,7 +742,9 @@ def kernel_case(name: str, reps: int) -> int:
             ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).int().contiguous()
             wts = torch.full((rows, top), 1.0 / top, device=dev)
             y = torch.zeros(rows, Wd, device=dev)
-            run = lambda i: K.moe_experts(x, ids, wts, gus[i % n_buf], dns[i % n_buf], y, top, 7.0)
+            # gate and up rows in blocks of 128 (random weights: the layout only chooses the kernels): the prompt's pairs run
+            # as grouped products of the tcgen05 tile kernel, the decode step's on mma.sync tiles
+            run = lambda i: K.moe_experts(x, ids, wts, gus[i % n_buf], dns[i % n_buf], y, top, 7.0, glu_block=128)
             if B > 1:
                 bytes_ = len(set(ids.flatten().tolist())) * 3.0 * F * Wd * 2
             else:

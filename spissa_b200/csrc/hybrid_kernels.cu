@@ -1390,7 +1390,7 @@ moe_down_kernel(const TA* __restrict__ act, const TW* __restrict__ wd, const int
 #define MM_BK 32
 #define MM_ROW 40
 template <bool GLU>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ Wt, long long w_stride,
                int N, int K, const int* __restrict__ sorted, const int* __restrict__ tiles, int top,
                __nv_bfloat16* __restrict__ act, float* __restrict__ out, const float* __restrict__ wts, float limit,
@@ -1411,19 +1411,32 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = (K + MM_BK - 1) / MM_BK;
 
+    // a thread's 16-byte pieces of the two tiles are the same in every block of K: their rows' addresses are found once
+    constexpr int A_PIECES = MM_TM * 4 / 128, B_PIECES = (GLU ? 2 : 1) * MM_BN * 4 / 128;
+    int a_src[A_PIECES], b_src[B_PIECES];             // element offsets from A and from the expert's weights; -1: zeros
+#pragma unroll
+    for (int i = 0; i < A_PIECES; ++i) {
+        const int c = threadIdx.x + i * 128, src = src_row[c >> 2];
+        a_src[i] = src >= 0 ? src * lda + (c & 3) * 8 : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < B_PIECES; ++i) {
+        const int c = threadIdx.x + i * 128, m = c / (MM_BN * 4), n = n0 + ((c >> 2) % MM_BN);
+        const int w_row = blk ? (n / blk) * 2 * blk + n % blk + m * blk : m * N + n;
+        b_src[i] = n < N ? w_row * K + (c & 3) * 8 : -1;
+    }
     auto load = [&](int kb, int st) {
-        for (int c = threadIdx.x; c < MM_TM * 4; c += 128) {
-            const int r = c >> 2, k = kb * MM_BK + (c & 3) * 8;
-            const int src = src_row[r];
-            if (src >= 0 && k < K) cp_async16(smem_u32(&As[st][r][(c & 3) * 8]), A + (size_t)src * lda + k);
-            else *(uint4*)&As[st][r][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < A_PIECES; ++i) {
+            const int c = threadIdx.x + i * 128, k = kb * MM_BK + (c & 3) * 8;
+            if (a_src[i] >= 0 && k < K) cp_async16(smem_u32(&As[st][c >> 2][(c & 3) * 8]), A + a_src[i] + kb * MM_BK);
+            else *(uint4*)&As[st][c >> 2][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
         }
-        for (int c = threadIdx.x; c < (GLU ? 2 : 1) * MM_BN * 4; c += 128) {
-            const int m = c / (MM_BN * 4), r = (c >> 2) % MM_BN, k = kb * MM_BK + (c & 3) * 8;
-            const int n = n0 + r;
-            const size_t w_row = blk ? (size_t)(n / blk) * 2 * blk + n % blk + (size_t)m * blk : (size_t)m * N + n;
-            if (n < N && k < K) cp_async16(smem_u32(&Bs[st][m][r][(c & 3) * 8]), w0 + w_row * K + k);
-            else *(uint4*)&Bs[st][m][r][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < B_PIECES; ++i) {
+            const int c = threadIdx.x + i * 128, k = kb * MM_BK + (c & 3) * 8;
+            if (b_src[i] >= 0 && k < K) cp_async16(smem_u32(&Bs[st][c / (MM_BN * 4)][(c >> 2) % MM_BN][(c & 3) * 8]), w0 + b_src[i] + kb * MM_BK);
+            else *(uint4*)&Bs[st][c / (MM_BN * 4)][(c >> 2) % MM_BN][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
         }
         cp_async_commit();
     };
@@ -1508,6 +1521,8 @@ SP_API int sp_moe_experts(const void* x, int x_dt, const int* ids, const void* w
         SP_FAIL("moe_experts: gate and up rows in blocks of %d are a bfloat16 layout for sizes that are multiples of it", glu_block);
     const bool mma = x_dt == SP_DT_BF16 && w_dt == SP_DT_BF16 && W % 8 == 0 && F % 8 == 0 &&
                      (((uintptr_t)x | (uintptr_t)wgu | (uintptr_t)wd | (uintptr_t)act) & 15) == 0;
+    if (mma && ((long long)T * W >= (1LL << 31) || (long long)n_pairs * F >= (1LL << 31) || 2LL * F * W >= (1LL << 31)))
+        SP_FAIL("moe_experts: operands beyond 2^31 elements");
     const int tm = mma ? MM_TM : ME_TM;
     if ((n_pairs + tm - 1) / tm + E > max_tiles) SP_FAIL("moe_experts: the tile table is too short");
     if (moe_plan(ids, n_pairs, E, counts, sorted, tiles, max_tiles, tm, stream)) return 1;

@@ -463,6 +463,33 @@ def test_every_cut_agrees_with_plain(models, name, dtype, tmp_path):
         compare(results[cut], results["whole"], tol, f"{name}/{dtype}: {cut} against whole", allow)
 
 
+def test_a_long_prompt_takes_the_grouped_expert_products_and_decoding_the_small_tiles(tmp_path):
+    """A width and expert size that the tcgen05 tile kernel takes: a prompt of 300 tokens (600 pairs) runs its experts
+    as grouped products, the decode steps behind it on the mma.sync tiles, the 32-bit mode on FFMA tiles; all agree with
+    the plain implementation."""
+    from spissa_b200.csrc import lib as K
+    cfg = model(128, 180, [par(left(4, 2, 32, 32, conv=3, rot=16, window=100), 2, 16, 32, 8.0, 0.8, 0.6),
+                           par(left(2, 2, 64, 64, conv=2, rot=64, window=40), 1, 32, 64, 4.0, 1.0, 1.0)],
+                [moe(8, 2, 64, 2.0, groups=(2, 1), shared=(64, 2.0)), moe(4, 3, 128, 1.0)], streams=2)
+    pcfg, w = make(cfg, tmp_path, seed=41, std=0.07, norm_std=0.1)
+    m = SimpleNamespace(cfg=pcfg, w=w)
+    toks = tiny.random_prompt(180, 330, 8)
+    ref = logits_of(m, toks)
+    for dtype, tol, allow in (("float32", 2e-5, 0.0), ("bfloat16", 3e-2, CLOSE_CALLS)):
+        eng = Engine.from_folder(str(tmp_path), dtype=dtype, max_tokens=64 * 7, max_seqs=1)
+        before = K.launches
+        s = eng.acquire()
+        rows = [eng.step([(s, toks[:300], list(range(300)))]).cpu()]
+        rows += [eng.step([(s, [t], [0])]).cpu() for t in toks[300:]]
+        eng.release(s)
+        got = {("p", i): r for i, r in enumerate(torch.cat(rows))}
+        compare(got, {("p", i): r for i, r in enumerate(ref)}, tol, dtype, allow)
+        if dtype == "bfloat16":
+            layer = eng.model.layers[0].ffn
+            assert layer.glu_block == 64 and eng.model.layers[1].ffn.glu_block == 128
+    assert "tc_gemm" in K.loaded_libraries()
+
+
 @pytest.mark.parametrize("name", ["a", "d"])
 def test_portions_of_a_prompt_down_to_two_tokens(models, name):
     m = models[name]
