@@ -109,7 +109,7 @@ class HyperConnectionBlock(Block):
 
         a = norm_q(Σ_s in_q[s] X_s);   y = sublayer_q(a);   X_t ← Σ_s mix_q[s, t] X_s + out_q[t] · y   (all t at once)
 
-    The sublayers keep their contract: they ADD into a 32-bit row buffer, which is zero when they get it. One kernel
+    The sublayers keep their interface: they ADD into a 32-bit row buffer, which is zero when they get it. One kernel
     takes y into the streams, leaves the buffer zeroed and norms the next sublayer's input; the norms must describe
     themselves as layer norms (``fused_fields()`` kind ``layernorm``). ``names``: the tensors' names behind the prefix
     (``in1``, ``out1``, ``mix1``, ``in2``, ``out2``, ``mix2``)."""
