@@ -686,14 +686,12 @@ __global__ void __launch_bounds__(256) gla_chunk_prep_kernel(GlcArgs c) {
     float* kT = qT + (size_t)d * GLC_TS;      // [d][GLC_TS]
     float* bT = kT + (size_t)d * GLC_TS;      // [d][GLC_TS]  B
     float* rr = bT + (size_t)d * GLC_TS;      // [GLC][rank]
-    float* A2 = rr + (size_t)GLC * rank;      // [d][rank]
     int s, t0, n;
     if (!glc_chunk_of(a, blockIdx.x, s, t0, n)) return;
     const int h = blockIdx.y;
     const int Hd = a.H * d, Hv = a.H * a.vd;
     const float qscale = 1.0f / sqrtf((float)d);
     for (int e = threadIdx.x; e < n * rank; e += blockDim.x) rr[e] = a.proj[(size_t)(t0 + e / rank) * a.ld + 2 * Hd + 2 * Hv + e % rank];
-    for (int e = threadIdx.x; e < d * rank; e += blockDim.x) A2[e] = sp_ld_dt(a.a2, a.w_dt, (size_t)h * d * rank + e);
     for (int x = threadIdx.x; x < GLC * d; x += blockDim.x) {
         const int i = x / d, e = x % d;
         const bool in = i < n;
@@ -702,15 +700,23 @@ __global__ void __launch_bounds__(256) gla_chunk_prep_kernel(GlcArgs c) {
         kT[e * GLC_TS + i] = in ? row[Hd + h * d + e] : 0.0f;
     }
     __syncthreads();
+    // every token's and channel's log decay by all threads, then the running sums by one thread per channel
+    for (int x = threadIdx.x; x < GLC * d; x += blockDim.x) {
+        const int e = x / GLC, i = x % GLC;
+        float la = 0.0f;
+        if (i < n) {
+            float z = sp_ld_dt(a.a2b, a.w_dt, h * d + e);
+            // a warp's threads share the channel: its row of the decay projection comes as one broadcast load each
+            for (int r = 0; r < rank; ++r) z = fmaf(sp_ld_dt(a.a2, a.w_dt, ((size_t)h * d + e) * rank + r), rr[i * rank + r], z);
+            la = (fminf(z, 0.0f) - log1pf(expf(-fabsf(z)))) * a.inv_tau;
+        }
+        bT[e * GLC_TS + i] = la;
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < d; e += blockDim.x) {
-        const float bias = sp_ld_dt(a.a2b, a.w_dt, h * d + e);
         float run = 0.0f;
         for (int i = 0; i < GLC; ++i) {
-            if (i < n) {
-                float z = bias;
-                for (int r = 0; r < rank; ++r) z = fmaf(A2[e * rank + r], rr[i * rank + r], z);
-                run += (fminf(z, 0.0f) - log1pf(expf(-fabsf(z)))) * a.inv_tau;
-            }
+            run += bT[e * GLC_TS + i];
             bT[e * GLC_TS + i] = run;                            // beyond the chunk's tokens: B_last
         }
     }
@@ -782,7 +788,7 @@ __global__ void __launch_bounds__(256) gla_chunk_sum_kernel(GlcArgs c) {
     int s, t0, n;
     if (!glc_chunk_of(a, blockIdx.x, s, t0, n)) return;
     const int h = blockIdx.y, c0 = blockIdx.z * 64;
-    const int Hd = a.H * d, Hv = a.H * vd;
+    const int Hd = a.H * d;
     for (int x = threadIdx.x; x < GLC * DP; x += blockDim.x) {
         const int j = x / DP, e = x % DP;
         kd[x] = (j < n && e < d) ? c.ke[(size_t)(t0 + j) * Hd + h * d + e] : 0.0f;
@@ -822,12 +828,21 @@ __global__ void __launch_bounds__(256) gla_chunk_scan_kernel(GlcArgs c) {
     float* st = a.state + ((size_t)slot * a.H + h) * a.d * a.vd + x;
     float S = *st;
     const int e = x / a.vd;
-#pragma unroll 8
-    for (int k = 0; k < nc; ++k) {                   // the loads do not depend on S: several chunks' are in flight
-        float* slot_k = c.cs + ((size_t)(first_chunk + k) * a.H + h) * a.d * a.vd + x;
-        const float own = *slot_k;
-        *slot_k = S;
-        S = fmaf(c.dl[((size_t)(first_chunk + k) * a.H + h) * a.d + e], S, own);
+    // eight chunks' sums and decays are asked for together (they do not depend on S), then taken in order
+    for (int k0 = 0; k0 < nc; k0 += 8) {
+        float own[8], dv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (k0 + u < nc) {
+                own[u] = c.cs[((size_t)(first_chunk + k0 + u) * a.H + h) * a.d * a.vd + x];
+                dv[u] = c.dl[((size_t)(first_chunk + k0 + u) * a.H + h) * a.d + e];
+            }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (k0 + u < nc) {
+                c.cs[((size_t)(first_chunk + k0 + u) * a.H + h) * a.d * a.vd + x] = S;
+                S = fmaf(dv[u], S, own[u]);
+            }
     }
     *st = S;
 }
@@ -908,7 +923,7 @@ SP_API int sp_gla_chunked(const float* proj, int ld, float* state, int n_slots, 
     c.g.o_raw = c.cs + glc_up4((long long)n_chunks * H * d * vd);
     c.n_chunks = n_chunks;
     const int MA = d <= 64 ? 1 : 2, DP = 64 * MA;
-    const size_t smem1 = (3 * (size_t)d * GLC_TS + (size_t)GLC * rank + (size_t)d * rank) * sizeof(float);
+    const size_t smem1 = (3 * (size_t)d * GLC_TS + (size_t)GLC * rank) * sizeof(float);       // two CTAs per SM at d = 128
     const size_t smem2 = ((size_t)GLC * DP + GLC * 64) * sizeof(float);
     const size_t smem4 = ((size_t)DP * GLC_TS + (size_t)DP * 64 + 2 * GLC * 64) * sizeof(float);
     if (!gla_chunk_ready.done()) {
@@ -1404,8 +1419,10 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
     if (e < 0) return;
     const int first = tiles[blockIdx.x * 3 + 1], rows = tiles[blockIdx.x * 3 + 2];
     const int n0 = blockIdx.y * MM_BN;
-    if (threadIdx.x < MM_TM)
-        src_row[threadIdx.x] = threadIdx.x < rows ? (GLU ? sorted[first + threadIdx.x] / top : first + threadIdx.x) : -1;
+    if (threadIdx.x < MM_TM) {
+        const int m = (int)threadIdx.x;
+        src_row[m] = m < rows ? (GLU ? sorted[first + m] / top : first + m) : -1;
+    }
     __syncthreads();
     const __nv_bfloat16* w0 = Wt + (size_t)e * w_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
