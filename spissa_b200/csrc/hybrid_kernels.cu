@@ -1395,7 +1395,8 @@ moe_down_kernel(const TA* __restrict__ act, const TW* __restrict__ wd, const int
 }
 
 // The same products on the tensor cores (bfloat16 operands, 32-bit accumulators): tiles of 128 rows x 64 columns, K in
-// blocks of 32 through two shared-memory stages filled by cp.async; four warps, each 32 rows x all columns with
+// blocks of 32 through three shared-memory stages filled by cp.async (two in flight while one is multiplied: a decode
+// step's tiles are bound by how many bytes a CTA has asked for); four warps, each 32 rows x all columns with
 // mma.sync m16n8k16 (A and B fragments by ldmatrix from rows padded to 80 bytes); a group of 16 rows beyond the tile's
 // rows (a decode step's tiles hold a row or two) is skipped. GLU: the tile holds the gate and the
 // up columns of the same outputs and stores the activation; else the result times the pair's weight goes to the
@@ -1404,6 +1405,9 @@ moe_down_kernel(const TA* __restrict__ act, const TW* __restrict__ wd, const int
 #define MM_BN 64
 #define MM_BK 32
 #define MM_ROW 40
+#define MM_STAGES 3
+template <bool GLU>
+constexpr size_t mm_smem_bytes() { return (size_t)MM_STAGES * (MM_TM + (GLU ? 2 : 1) * MM_BN) * MM_ROW * sizeof(__nv_bfloat16); }
 template <bool GLU>
 __global__ void __launch_bounds__(128, 3)
 moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ Wt, long long w_stride,
@@ -1412,8 +1416,11 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
                float slope, int blk) {
     // ``blk`` (GLU): 0 = an expert's N gate rows, then its N up rows; else blocks of ``blk`` gate rows, each followed by
     // the ``blk`` up rows of the same outputs (the layout the tcgen05 tile kernel's gated epilogue reads)
-    __shared__ __align__(16) __nv_bfloat16 As[2][MM_TM][MM_ROW];
-    __shared__ __align__(16) __nv_bfloat16 Bs[2][GLU ? 2 : 1][MM_BN][MM_ROW];
+    extern __shared__ __align__(16) unsigned char mm_smem[];
+    typedef __nv_bfloat16 (*ATile)[MM_TM][MM_ROW];
+    typedef __nv_bfloat16 (*BTile)[GLU ? 2 : 1][MM_BN][MM_ROW];
+    ATile As = (ATile)mm_smem;                                                              // [stages][rows][k]
+    BTile Bs = (BTile)(mm_smem + (size_t)MM_STAGES * MM_TM * MM_ROW * sizeof(__nv_bfloat16));   // [stages][gate / up][columns][k]
     __shared__ int src_row[MM_TM];
     const int e = tiles[blockIdx.x * 3];
     if (e < 0) return;
@@ -1442,9 +1449,11 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
         const int w_row = blk ? (n / blk) * 2 * blk + n % blk + m * blk : m * N + n;
         b_src[i] = n < N ? w_row * K + (c & 3) * 8 : -1;
     }
+    const int a_rows = (rows + 15) / 16 * 16;
     auto load = [&](int kb, int st) {
 #pragma unroll
         for (int i = 0; i < A_PIECES; ++i) {
+            if (32 * i >= a_rows) break;                       // groups of rows that no product reads stay as they are
             const int c = threadIdx.x + i * 128, k = kb * MM_BK + (c & 3) * 8;
             if (a_src[i] >= 0 && k < K) cp_async16(smem_u32(&As[st][c >> 2][(c & 3) * 8]), A + a_src[i] + kb * MM_BK);
             else *(uint4*)&As[st][c >> 2][(c & 3) * 8] = make_uint4(0, 0, 0, 0);
@@ -1460,17 +1469,31 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
 
     float acc[2][GLU ? 2 : 1][8][4] = {};
     const bool live[2] = {warp * 32 < rows, warp * 32 + 16 < rows};
+    const bool narrow = rows <= 16;
     load(0, 0);
+    if (nk > 1) load(1, 1);
     for (int kb = 0; kb < nk; ++kb) {
-        if (kb + 1 < nk) {
-            load(kb + 1, (kb + 1) & 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const int st = kb & 1;
-        if (live[0]) {
+        if (kb + 1 < nk) cp_async_wait<1>();          // block kb has landed; block kb + 1 may still be on its way
+        else cp_async_wait<0>();
+        __syncthreads();                                // ... for every thread's pieces, and block kb - 1 is done with
+        if (kb + 2 < nk) load(kb + 2, (kb + 2) % MM_STAGES);
+        const int st = kb % MM_STAGES;
+        if (narrow) {
+            // at most 16 rows (a decode step's tile): the four warps share the columns instead of the rows; warp w owns
+            // column tiles 2w and 2w + 1 and keeps them in the accumulators' first two places
+#pragma unroll
+            for (int k16 = 0; k16 < MM_BK / 16; ++k16) {
+                uint32_t a[4];
+                ldmatrix_x4(smem_u32(&As[st][lane & 15][k16 * 16 + (lane >> 4) * 8]), a[0], a[1], a[2], a[3]);
+#pragma unroll
+                for (int m = 0; m < (GLU ? 2 : 1); ++m) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(smem_u32(&Bs[st][m][warp * 16 + (lane & 7) + (lane >> 4) * 8][k16 * 16 + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
+                    mma_bf16(acc[0][m][0], a, b0, b1);
+                    mma_bf16(acc[0][m][1], a, b2, b3);
+                }
+            }
+        } else if (live[0]) {
 #pragma unroll
             for (int k16 = 0; k16 < MM_BK / 16; ++k16) {
                 uint32_t a[2][4];
@@ -1493,7 +1516,26 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16
                     }
             }
         }
-        __syncthreads();
+    }
+    if (narrow) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = (lane >> 2) + 8 * half;
+            if (m >= rows) continue;
+            const int p = GLU ? 0 : sorted[first + m];
+            const float wt = GLU ? 0.0f : wts[p];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int n = n0 + (2 * warp + j) * 8 + (lane & 3) * 2;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (n + u >= N) continue;
+                    if (GLU) act[(size_t)(first + m) * N + n + u] = __float2bfloat16_rn(hy_clamped_glu(acc[0][0][j][2 * half + u], acc[0][GLU ? 1 : 0][j][2 * half + u], limit, slope));
+                    else out[(size_t)p * N + n + u] = acc[0][0][j][2 * half + u] * wt;
+                }
+            }
+        }
+        return;
     }
 #pragma unroll
     for (int f = 0; f < 2; ++f)
@@ -1545,11 +1587,18 @@ SP_API int sp_moe_experts(const void* x, int x_dt, const int* ids, const void* w
     if (moe_plan(ids, n_pairs, E, counts, sorted, tiles, max_tiles, tm, stream)) return 1;
     if (mma) {
         const int used = (n_pairs + tm - 1) / tm + E;           // entries beyond the tiles in use say expert -1
-        moe_mma_kernel<true><<<dim3(used, (F + MM_BN - 1) / MM_BN), 128, 0, stream>>>(
+        static SpPerDevice mma_ready;
+        if (!mma_ready.done()) {
+            if (cudaFuncSetAttribute(moe_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mm_smem_bytes<true>()) != cudaSuccess ||
+                cudaFuncSetAttribute(moe_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mm_smem_bytes<false>()) != cudaSuccess)
+                SP_FAIL("moe_experts: cannot raise the shared memory limit");
+            mma_ready.mark();
+        }
+        moe_mma_kernel<true><<<dim3(used, (F + MM_BN - 1) / MM_BN), 128, mm_smem_bytes<true>(), stream>>>(
             (const __nv_bfloat16*)x, W, (const __nv_bfloat16*)wgu, 2LL * F * W, F, W, sorted, tiles, top,
             (__nv_bfloat16*)act, nullptr, nullptr, limit, slope, glu_block);
         SP_CHECK_LAUNCH("moe_up (tensor cores)");
-        moe_mma_kernel<false><<<dim3(used, (W + MM_BN - 1) / MM_BN), 128, 0, stream>>>(
+        moe_mma_kernel<false><<<dim3(used, (W + MM_BN - 1) / MM_BN), 128, mm_smem_bytes<false>(), stream>>>(
             (const __nv_bfloat16*)act, F, (const __nv_bfloat16*)wd, (long long)W * F, W, F, sorted, tiles, top, nullptr,
             out_pairs, wts, 0.0f, 0.0f, 0);
         SP_CHECK_LAUNCH("moe_down (tensor cores)");
